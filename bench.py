@@ -1,0 +1,337 @@
+#!/usr/bin/env python
+"""Benchmark of the int4 dequant-matmul path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+One STEP is one pass of the hot path over a rotation of distinct weight sets (together larger than the
+126 MB L2, so every launch streams its weights from HBM); the launches of a step are replayed from a CUDA
+graph so host launch cost does not enter the device-timed number. Rank 0 prints one JSON line.
+
+Workloads
+  prefill_gemm_m512  X[512,2048] f16 times int4 W[8192,2048] (group 64, affine), f16 out. TFLOP/s. (default)
+  decode_gemv        x[1,2048] times the same weight format, GB/s of algorithmic bytes.
+  decode_layer_set   the 8B-class projections at M=1 (q,k,v,o,gate,up,down,lm_head), GB/s.
+
+With N > 1 every rank runs its own replica of the workload on its own weight sets (the single GEMM / GEMV
+does not shard); value is the aggregate over ranks divided by the slowest rank's device time.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "int4 matmul HBM GB/s (decode M=1) and TFLOP/s (prefill M=512) vs roofline"
+L2_BYTES = 126 * 1024 * 1024
+
+
+def algorithmic_bytes(N, K, M, bits=4, group=64, affine=True, out_bytes=2):
+    """weights + scales (+ biases) + activations + outputs, each touched once."""
+    return N * K * bits // 8 + (2 if affine else 1) * (N * K // group) * 2 + M * K * 2 + M * N * out_bytes
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(hbm=d["hbm_gbs"], tf_burst=d["bf16_tflops"], tf_sustained=d.get("bf16_tflops_sustained"),
+                    src="measured")
+    return dict(hbm=6650.0, tf_burst=1590.0, tf_sustained=1400.0, src="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows, self.proc, self.index = [], None, index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        ok = [r for r in self.rows if len(r) >= 8 and r[0].isdigit()]
+        if not ok:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        reasons = set()
+        for r in ok:
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median([int(r[0]) for r in ok])), "sm_max_mhz": float(ok[0][1]),
+                "power_w_max": max(float(r[2]) for r in ok), "samples": len(ok), "reasons": sorted(reasons)}
+
+
+# ---------------------------------------------------------------------------------------------------
+def workload_shapes(name):
+    """(label, N, K, M, out_f32) launches of one rotation element."""
+    import zero_tvm_b200 as z
+    if name == "prefill_gemm_m512":
+        return [("W[8192,2048] M=512", 8192, 2048, 512, False)]
+    if name == "decode_gemv":
+        return [("W[8192,2048] M=1", 8192, 2048, 1, False)]
+    if name == "decode_layer_set":
+        return [(n, N, K, 1, f32) for n, N, K, f32 in z.synth.DENSE_LAYER_SET]
+    raise SystemExit(f"unknown workload {name}")
+
+
+def make_sets(shapes, seed, torch, device):
+    """Distinct weight sets until one rotation exceeds 4x L2 (codes random; scales/biases as the configs say)."""
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    per_set = sum(algorithmic_bytes(N, K, 1) for _, N, K, _, _ in shapes)
+    R = max(2, int(np.ceil(4 * L2_BYTES / per_set)))
+    sets = []
+    for _ in range(R):
+        one = []
+        for _, N, K, M, f32 in shapes:
+            W = torch.randint(-2**31, 2**31 - 1, (N, K // 8), dtype=torch.int32, device=device, generator=g)
+            s = (torch.randn((N, K // 64), device=device, generator=g) * 0.01).abs().to(torch.float16)
+            b = (torch.randn((N, K // 64), device=device, generator=g) * 0.05).to(torch.float16)
+            y = torch.empty((M, N), dtype=torch.float32 if f32 else torch.float16, device=device)
+            one.append((W, s, b, y))
+        sets.append(one)
+    return sets, R
+
+
+def cpu_baseline(shapes, budget_s=12.0):
+    """The oracle's reference-order CPU matmul (C, OpenMP, all host threads) on a bounded sample."""
+    import zero_tvm_b200 as z
+    from oracle import ztvm_oracle_c as zc
+    zc.build()
+    label, N, K, M, f32 = shapes[0]
+    Ms = min(M, 16)
+    p = z.synth.projection(N, K, M=Ms, seed=0)
+    zc.gemv_ref(p["x"], p["W"], p["scales"], p["biases"], 64, out_f32=f32)  # warm
+    t0, n = time.perf_counter(), 0
+    while True:
+        zc.gemv_ref(p["x"], p["W"], p["scales"], p["biases"], 64, out_f32=f32)
+        n += 1
+        dt = time.perf_counter() - t0
+        if dt > budget_s or n >= 50:
+            break
+    per = dt / n
+    return dict(seconds_per_sample=per, rows=Ms, N=N, K=K, cores=zc.num_threads(),
+                sample=f"{n} x ({label.split()[0]} with M={Ms} of {M} rows), reference word order, C/OpenMP")
+
+
+def run_reference_arm(args, rank):
+    """The reference's CPU-side arithmetic for this path (its WGSL cannot run without WebGPU): the oracle's C
+    restatement, all host threads, on a bounded sample of the same workload."""
+    if rank != 0:
+        return
+    shapes = workload_shapes(args.workload)
+    is_gemm = shapes[0][3] > 8
+    vals = []
+    for _ in range(max(1, args.steps)):
+        cb = cpu_baseline(shapes, budget_s=max(2.0, 20.0 / max(1, args.steps)))
+        label, N, K, M, f32 = shapes[0]
+        if is_gemm:
+            vals.append(2.0 * cb["rows"] * N * K / cb["seconds_per_sample"] / 1e12)
+        else:
+            vals.append(algorithmic_bytes(N, K, cb["rows"]) / cb["seconds_per_sample"] / 1e9)
+    v = float(np.median(vals))
+    unit = "TFLOP/s" if is_gemm else "GB/s"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": v, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": cb["seconds_per_sample"] * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16 x int4 -> f32 accumulate", "data": "synthetic",
+        "config": {"workload": args.workload, "shape": shapes[0][0]},
+        "cpu_baseline": {"value": v, "unit": unit, "cores": cb["cores"], "kind": "port", "sample": cb["sample"]},
+        "e2e": {"value": v, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="prefill_gemm_m512")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(3, args.warmup)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+
+    import torch
+    import zero_tvm_b200 as z
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+    ctx = z.Context(local)
+
+    shapes = workload_shapes(args.workload)
+    is_gemm = shapes[0][3] > 8
+    sets, R = make_sets(shapes, 1234 + rank, torch, device)
+    xs = [torch.randn((M, K), device=device).to(torch.float16) for _, N, K, M, _ in shapes]
+    descs = [z.MmDesc(K, N, M, 64, 4, 1, int(f32)) for _, N, K, M, f32 in shapes]
+    stream = torch.cuda.Stream(device)
+
+    def one_pass():
+        for one in sets:
+            for (W, s, b, y), x, d in zip(one, xs, descs):
+                ctx.int4_matmul(d, y, x, s, W, b, stream)
+
+    launches_per_matmul = [max(1, (M + 7) // 8) if True else 1 for _, N, K, M, _ in shapes]
+    with torch.cuda.stream(stream):
+        one_pass()                      # sets function attributes outside of capture
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            one_pass()
+        for _ in range(args.warmup):
+            graph.replay()
+        stream.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local) as clocks:
+            ev0.record(stream)
+            for _ in range(args.steps):
+                graph.replay()
+            ev1.record(stream)
+            stream.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1)
+    if world > 1:
+        t = torch.tensor([ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / args.steps
+    n_launch_step = R * sum(launches_per_matmul)
+
+    flops_step = R * sum(2.0 * M * N * K for _, N, K, M, _ in shapes)
+    bytes_step = R * sum(algorithmic_bytes(N, K, M, out_bytes=4 if f32 else 2) for _, N, K, M, f32 in shapes)
+    peaks = measured_peaks()
+    if is_gemm:
+        value = world * flops_step / (ms_per_step * 1e-3) / 1e12
+        unit = "TFLOP/s"
+        peak = peaks["tf_sustained"] or peaks["tf_burst"]
+        roof = {"bound": "tensor", "achieved": flops_step / (ms_per_step * 1e-3) / 1e12, "peak": peak,
+                "unit": "TFLOP/s", "peak_kind": f"{peaks['src']} sustained bf16 (kernel timed inside a long step)"}
+    else:
+        value = world * bytes_step / (ms_per_step * 1e-3) / 1e9
+        unit = "GB/s"
+        roof = {"bound": "hbm", "achieved": bytes_step / (ms_per_step * 1e-3) / 1e9, "peak": peaks["hbm"],
+                "unit": "GB/s", "peak_kind": f"{peaks['src']} copy bandwidth"}
+    roof["frac"] = roof["achieved"] / roof["peak"]
+    roof["traffic"] = None
+    roof["avg_launch_us"] = ms_per_step * 1e3 / (R * len(shapes))
+
+    # ---- correctness of the timed configuration (a skipped dispatch always looks like a fast one) ----
+    W, s, b, y = sets[0][0]
+    label, N, K, M, f32 = shapes[0]
+    torch.cuda.synchronize()
+    yh = y.float().cpu().numpy()
+    verified = None
+    if rank == 0:
+        from oracle import ztvm_oracle_c as zc
+        zc.build()
+        rows = min(M, 4)
+        y64 = zc.matmul_f64(xs[0][:rows].cpu().numpy(), W.cpu().numpy().view(np.uint32), s.cpu().numpy(),
+                            b.cpu().numpy(), 64)
+        err = float(np.max(np.abs(yh[:rows] - y64) / np.maximum(np.abs(y64), 1e-3)))
+        verified = {"rows": rows, "max_rel_err": err, "ok": bool(err <= 2e-3 and np.abs(yh).max() > 0)}
+
+    # ---- end to end through the host-buffer entry point: pinned x in, y out, every launch ----
+    d0 = descs[0]
+    xh = torch.randn((M, K)).to(torch.float16).pin_memory()
+    yh_t = torch.empty((M, N), dtype=torch.float32 if f32 else torch.float16).pin_memory()
+    e2e_sets = [one[0] for one in sets]
+    for (W, s, b, _y) in e2e_sets[:3]:
+        ctx.int4_matmul_host(d0, yh_t, xh, s, W, b)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e2e_steps = max(1, min(args.steps, 5))
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        for (W, s, b, _y) in e2e_sets:
+            ctx.int4_matmul_host(d0, yh_t, xh, s, W, b)
+    torch.cuda.synchronize()
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_s], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    if is_gemm:
+        e2e_val = world * R * 2.0 * M * N * K / e2e_s / 1e12
+    else:
+        e2e_val = world * R * algorithmic_bytes(N, K, M, out_bytes=4 if f32 else 2) / e2e_s / 1e9
+    e2e = {"value": e2e_val, "unit": unit, "h2d_bytes_per_step": R * M * K * 2,
+           "d2h_bytes_per_step": R * M * N * (4 if f32 else 2),
+           "what": "ztvm_int4_matmul_host per launch: pinned x -> device, kernel, y -> host, sync; weights resident"}
+
+    out = {
+        "metric": METRIC, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f16 x int4 -> f32 accumulate", "data": "synthetic",
+        "config": {"workload": args.workload, "shapes": [s_[0] for s_ in shapes], "group": 64, "bits": 4,
+                   "rotation_sets": R, "rotation_bytes": int(bytes_step),
+                   "l2": "inputs larger than L2: weight sets rotate, 4x L2 per step",
+                   "parallelism": "replicas" if world > 1 else "single"},
+        "roofline": roof, "e2e": e2e, "gpu_launches": int(args.steps * n_launch_step),
+        "clocks": clocks.summary(), "verified": verified,
+    }
+    if rank == 0:
+        if not args.no_cpu_baseline:
+            cb = cpu_baseline(shapes)
+            if is_gemm:
+                v = 2.0 * cb["rows"] * cb["N"] * cb["K"] / cb["seconds_per_sample"] / 1e12
+            else:
+                v = algorithmic_bytes(cb["N"], cb["K"], cb["rows"]) / cb["seconds_per_sample"] / 1e9
+            out["cpu_baseline"] = {"value": v, "unit": unit, "cores": cb["cores"], "kind": "port", "sample": cb["sample"]}
+        print(json.dumps(out))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

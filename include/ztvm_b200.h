@@ -1,0 +1,153 @@
+/* ztvm_b200.h — C ABI of libztvm_b200.so: CUDA (sm_100a) replacements for the Zero-TVM
+ * int4 / int3 group-quantised dequant-matmul kernels and the MoE glue around them.
+ *
+ * The reference engine (TypeScript + WGSL over WebGPU) has no FFI today. Its seam for this
+ * path is internal: a compute pipeline per kernel variant, a bind group
+ * [out, in, scales, weights, PODArgs, biases?, ids?] per call site
+ * (src/zero-tvm/engine-core.ts:76-92, :1699-1703) and
+ * dispatch(enc, pipeline, bindGroup, wgX, wgY, wgZ, label) (src/zero-tvm/engine-core.ts:2151-2179).
+ * Each entry point below takes exactly that tuple: raw device addresses for the buffers and a
+ * small POD struct holding what the reference passes in PODArgs. Citations are file:line within
+ * the reference project.
+ *
+ * Conventions
+ *  - Every function returns a ztvm_status (0 = ok). Nothing throws, aborts or launches on
+ *    invalid input (the reference's WebGPU validation silently SKIPS a bad dispatch; here the
+ *    caller gets an error code before any launch).
+ *  - Buffer arguments are device addresses (what cudaMalloc returns). The library never
+ *    allocates or frees caller buffers. Unless stated otherwise a call is asynchronous on
+ *    `stream` (a cudaStream_t; NULL = the context's own stream) and performs no host sync.
+ *  - Layouts: packed weights u32[N][K*bits/32], 4-bit code i of a word at bits [4i,4i+4)
+ *    (src/compiler/shaders/int4_matmul.gen.ts:157-167); 3-bit code i of a row at bit 3i of the
+ *    row's LSB-first bitstream (int4_matmul.gen.ts:115-131); scales / biases f16[N][K/group];
+ *    x f16[M][K]; y f16[M][N] (f32 when out_f32). Expert stacks add a leading [experts] axis.
+ *  - A context is bound to one GPU and is not re-entrant (the engine is single-threaded per
+ *    device, src/zero-tvm/engine-lock.ts); distinct contexts are independent.
+ */
+#ifndef ZTVM_B200_H_
+#define ZTVM_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* The library is built with hidden visibility; only these entry points are exported. */
+#if defined(__GNUC__)
+#define ZTVM_API __attribute__((visibility("default")))
+#else
+#define ZTVM_API
+#endif
+
+typedef int32_t ztvm_status;
+enum {
+  ZTVM_OK = 0,
+  ZTVM_ERR_NULL_POINTER = 1,  /* a required pointer is NULL */
+  ZTVM_ERR_BAD_DIMS = 2,      /* K/N/M/group inconsistent with the layout rules */
+  ZTVM_ERR_UNSUPPORTED = 3,   /* combination the kernel family does not have (e.g. 3-bit symmetric) */
+  ZTVM_ERR_ALIGNMENT = 4,     /* buffer address not aligned as the kernel requires */
+  ZTVM_ERR_CUDA = 5,          /* a CUDA runtime call failed; see ztvm_last_error */
+  ZTVM_ERR_BAD_CONTEXT = 6,   /* NULL / destroyed context, or wrong device */
+  ZTVM_ERR_TOO_LARGE = 7      /* size beyond a stated limit of the entry point */
+};
+
+typedef struct ztvm_ctx ztvm_ctx;
+
+/* Library ABI version (major*100 + minor). */
+ZTVM_API int32_t ztvm_version(void);
+ZTVM_API const char* ztvm_status_string(ztvm_status s);
+
+/* One context per GPU: owns a stream, pinned staging and device workspace.
+ * Replaces compile(device, ...) creating the matmul pipelines (src/compiler/compiler.ts:319-454). */
+ZTVM_API ztvm_status ztvm_init(int32_t device_ordinal, ztvm_ctx** out_ctx);
+/* Replaces DecodeEngine.destroy() for the matmul resources (src/zero-tvm/engine-core.ts:5274-5313). */
+ZTVM_API ztvm_status ztvm_destroy(ztvm_ctx* ctx);
+/* Message of the last failing call on this thread (valid until the next call). ctx may be NULL. */
+ZTVM_API const char* ztvm_last_error(ztvm_ctx* ctx);
+/* Blocks until the context's own stream is idle. */
+ZTVM_API ztvm_status ztvm_sync(ztvm_ctx* ctx);
+
+/* What the reference passes as PODArgs {K_PACKED = K*bits/32, SCALES_PER_ROW = K/group, N, M_ROWS}
+ * (src/zero-tvm/engine-core.ts:787-794, :1021-1022, :4033-4038), given as logical dims. */
+typedef struct ztvm_mm_desc {
+  uint32_t K;       /* reduction length; K % group == 0 */
+  uint32_t N;       /* output features (weight rows) */
+  uint32_t M;       /* activation rows (1 = decode) */
+  uint32_t group;   /* 64 (MLX affine) or 32 (MLC symmetric) */
+  uint32_t bits;    /* 4 or 3 */
+  uint32_t affine;  /* 1: w = scale*q + bias   0: w = scale*(q-7), biases ignored */
+  uint32_t out_f32; /* 1: y is f32 (lm_head), 0: f16 */
+} ztvm_mm_desc;
+
+/* y = x * dequant(W)^T. Replaces every dispatch of an int4_matmul* pipeline on a dense projection:
+ * int4_matmul[_f32][_sg|_tiled|_tiled8][_vec4|_vec4h][_affine][_q3], int4_matmul_batched_m4,
+ * int4_matmul_batched_dyn[_affine] and the tiled / subgroup-matrix prefill GEMMs
+ * (src/compiler/shaders/int4_matmul.gen.ts:170-571, :580-695, :805-1456; call sites
+ * src/zero-tvm/engine-core.ts:2290, :2312, :2517-2519, :2543-2549, :4280-4293).
+ * M <= 8 runs the bandwidth-bound GEMV; larger M runs the tensor-core GEMM. */
+ZTVM_API ztvm_status ztvm_int4_matmul(ztvm_ctx* ctx, const ztvm_mm_desc* desc, void* y, const void* x,
+                             const void* scales, const void* packed_w, const void* biases, void* stream);
+
+/* Same call with HOST activations and HOST output: copies x to the device, runs, copies y back and
+ * waits. Weights, scales and biases stay device-resident, as they are in the engine
+ * (src/zero-tvm/engine-core.ts:5259-5267). Synchronous. */
+ZTVM_API ztvm_status ztvm_int4_matmul_host(ztvm_ctx* ctx, const ztvm_mm_desc* desc, void* y_host, const void* x_host,
+                                  const void* scales, const void* packed_w, const void* biases);
+
+/* The MoE PODArgs (src/compiler/shaders/int4_matmul.gen.ts:216-225; built at
+ * src/zero-tvm/engine-core.ts:1049-1056). Strides are in ELEMENTS of x / y. mm.M must be 1. */
+typedef struct ztvm_moe_desc {
+  ztvm_mm_desc mm;
+  uint32_t experts;         /* rows of the stacks, including the shared expert if present */
+  uint32_t slots;           /* top-K plus the shared slot (src/compiler/model-spec.ts:659-660) */
+  uint32_t tokens;          /* grid y of the reference dispatch */
+  uint32_t in_slot_stride;  /* 0 = every slot reads the same input (gate / up) */
+  uint32_t out_slot_stride;
+  uint32_t in_tok_stride;
+  uint32_t out_tok_stride;
+  uint32_t ids_stride;      /* ids[] entries per token */
+} ztvm_moe_desc;
+
+/* For every (token, slot): expert = ids[token*ids_stride + slot]; y[...] = x[...] * dequant(W[expert])^T.
+ * Replaces int4_matmul_tiled[_vec4h]_affine[_q3]_moe (int4_matmul.gen.ts:229-254; call sites
+ * src/zero-tvm/engine-core.ts:2342-2349, :4387-4390). ids outside [0, experts) make the pair a no-op
+ * and raise the context's device-side error counter (see ztvm_device_errors). */
+ZTVM_API ztvm_status ztvm_int4_matmul_moe(ztvm_ctx* ctx, const ztvm_moe_desc* desc, void* y, const void* x,
+                                 const void* scales, const void* packed_w, const void* biases,
+                                 const uint32_t* ids, void* stream);
+
+/* softmax over E routed experts -> top-K (ties to the lower index) -> optional renormalisation ->
+ * slot K = expert E with sigmoid(logit[E]) when has_shared. logits f32[tokens][E+has_shared] ->
+ * ids u32[tokens][K+has_shared], scores f32 same shape.
+ * Replaces moe_router_topk (src/compiler/shaders/moe_router_topk.wgsl:66-136). E <= 1024, K <= 32. */
+ZTVM_API ztvm_status ztvm_moe_route_topk(ztvm_ctx* ctx, uint32_t E, uint32_t K, uint32_t norm_topk, uint32_t has_shared,
+                                uint32_t tokens, uint32_t* ids, float* scores, const float* logits,
+                                void* stream);
+
+/* h[r][i] = f16(up * gate * 1/(1+exp(-gate))) over rows of [gate(ffn) | up(ffn)] f16.
+ * Replaces silu_mul (src/compiler/shaders/silu_mul.wgsl:26-44). */
+ZTVM_API ztvm_status ztvm_silu_mul(ztvm_ctx* ctx, uint32_t rows, uint32_t ffn, void* h, const void* gate_up, void* stream);
+
+/* out[t][i] = f16(sum_s scores[t][s] * f32(y_slots[t][s][i])).
+ * Replaces moe_combine (src/compiler/shaders/moe_combine.wgsl:32-44). */
+ZTVM_API ztvm_status ztvm_moe_combine(ztvm_ctx* ctx, uint32_t tokens, uint32_t slots, uint32_t d, void* out,
+                             const void* y_slots, const float* scores, void* stream);
+
+/* Parity hooks: materialise what the fused kernels never store, through the same device functions
+ * the kernels inline. codes u8[N][K]; w_out f32[N][K] (as_f16 = 0: fl32(s*q+b), the GEMV / f32-staged
+ * definition, int4_matmul.gen.ts:1001) or f16[N][K] (as_f16 = 1: f16_rne of that value, what the
+ * tensor-core GEMM feeds the MMA; equals scripts/make-dsv2-layer-ref.py:108-116). desc->M is ignored. */
+ZTVM_API ztvm_status ztvm_unpack_codes(ztvm_ctx* ctx, const ztvm_mm_desc* desc, uint8_t* codes, const void* packed_w,
+                              void* stream);
+ZTVM_API ztvm_status ztvm_dequant(ztvm_ctx* ctx, const ztvm_mm_desc* desc, void* w_out, int32_t as_f16, const void* scales,
+                         const void* packed_w, const void* biases, void* stream);
+
+/* Number of device-side argument faults (out-of-range expert ids) seen since the last call of this
+ * function; resets the counter. Synchronises the context's stream and `stream`. */
+ZTVM_API ztvm_status ztvm_device_errors(ztvm_ctx* ctx, void* stream, uint32_t* count);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ZTVM_B200_H_ */

@@ -1,0 +1,166 @@
+"""GPU parity of the MoE path: router top-k, ids-indirect expert matmuls, SiLU*up, weighted combine,
+composed exactly like the engine's seven dispatches (src/zero-tvm/engine-core.ts:2342-2349)."""
+import numpy as np
+import pytest
+
+import zero_tvm_b200 as z
+from oracle import ztvm_oracle as zo
+from zero_tvm_b200.backend import moe_down_pod_args, moe_gate_pod_args, resolve_matmul
+
+pytestmark = pytest.mark.gpu
+TOL, FLOOR = 2e-3, 1e-3
+
+
+def run_block(backend, dev, mb, K_top=8, bits=4):
+    """router -> gate, up -> silu -> down -> combine with the engine's buffers and PODArgs."""
+    T, E, d, ffn = mb["T"], mb["E"], mb["hidden"], mb["ffn"]
+    slots = K_top + int(mb["has_shared"])
+    x, logits = dev.put(mb["x"]), dev.put(mb["logits"])
+    ids = dev.empty((T, slots), np.uint32, fill=0x7FFFFFFF)
+    scores = dev.empty((T, slots), np.float32, fill=-999.0)
+    backend.moe_router_topk(ids, scores, logits, E, K_top, True, mb["has_shared"], T)
+    gate_up = dev.empty((T, slots, 2 * ffn), np.float16, fill=float("nan"))
+    ent_g = resolve_matmul(affine=True, K=d, moe=True, q3=bits == 3)
+    ent_d = resolve_matmul(affine=True, K=ffn, moe=True, q3=bits == 3)
+    gw, gs, gb = (dev.put(a) for a in mb["gate"])
+    uw, us, ub = (dev.put(a) for a in mb["up"])
+    dw, ds, db = (dev.put(a) for a in mb["down"])
+    grid = (ffn // 4, T, slots)
+    backend.dispatch(ent_g, [gate_up, x, gs, gw, moe_gate_pod_args(d, ffn, slots, bits), gb, ids], grid)
+    # `up` is the same kernel bound ffn elements into the buffer (engine-core.ts:2036-2043)
+    up_view = gate_up.view(-1)[ffn:]
+    backend.dispatch(ent_g, [up_view, x, us, uw, moe_gate_pod_args(d, ffn, slots, bits), ub, ids], grid)
+    h = dev.empty((T, slots, ffn), np.float16, fill=float("nan"))
+    backend.silu_mul(h, gate_up, T * slots, ffn)
+    y_slots = dev.empty((T, slots, d), np.float16, fill=float("nan"))
+    backend.dispatch(ent_d, [y_slots, h, ds, dw, moe_down_pod_args(d, ffn, slots, bits), db, ids], (d // 4, T, slots))
+    y = dev.empty((T, d), np.float16, fill=float("nan"))
+    backend.moe_combine(y, y_slots, scores, T, slots, d)
+    assert backend.ctx.device_errors() == 0
+    return dict(ids=dev.get(ids, np.uint32), scores=dev.get(scores), gate_up=dev.get(gate_up), h=dev.get(h),
+                y_slots=dev.get(y_slots), y=dev.get(y))
+
+
+def check_block(got, mb, oracle_c, K_top=8, bits=4):
+    T, E, d, ffn = mb["T"], mb["E"], mb["hidden"], mb["ffn"]
+    ids_ref, sc_ref = oracle_c.router_topk(mb["logits"], E, K_top, True, mb["has_shared"])
+    # routing: indices exact, scores 2e-6 (tests/kernels/run.mjs:333-336)
+    assert np.array_equal(got["ids"], ids_ref)
+    assert np.abs(got["scores"] - sc_ref).max() < 2e-6
+    # each stage against the f64 anchor computed from the GPU's own (already checked) inputs
+    g64 = oracle_c.moe_matmul_f64(mb["x"], *mb["gate"], ids_ref, ffn, d, 64, bits, in_per_slot=False)
+    u64 = oracle_c.moe_matmul_f64(mb["x"], *mb["up"], ids_ref, ffn, d, 64, bits, in_per_slot=False)
+    assert zo.rel_err(got["gate_up"][..., :ffn], g64, FLOOR) <= TOL
+    assert zo.rel_err(got["gate_up"][..., ffn:], u64, FLOOR) <= TOL
+    h_ref = oracle_c.silu_mul(got["gate_up"], ffn)
+    assert zo.rel_err(got["h"], h_ref.astype(np.float64), FLOOR) <= TOL
+    d64 = oracle_c.moe_matmul_f64(got["h"], *mb["down"], ids_ref, d, ffn, 64, bits, in_per_slot=True)
+    assert zo.rel_err(got["y_slots"], d64, FLOOR) <= TOL
+    y_ref = oracle_c.moe_combine(got["y_slots"], got["scores"])
+    assert np.array_equal(got["y"].view(np.uint16), y_ref.view(np.uint16))
+    assert np.isfinite(got["y"].astype(np.float32)).all()
+
+
+@pytest.mark.parametrize("E,K,norm,shared", [(256, 8, True, True), (128, 8, True, False), (64, 6, False, True),
+                                              (257, 8, True, False), (1000, 32, True, True), (8, 8, True, False)])
+def test_router_topk(E, K, norm, shared, backend, dev, oracle_c):
+    """makeMoeTopkTest (tests/kernels/run.mjs:284-345): logits uniform in [-4,4), indices exact, scores 2e-6,
+    and on the no-shared path the slot past K stays untouched (poisoned here, as there)."""
+    rng = np.random.default_rng(E + K)
+    T = 37
+    logits = (rng.random((T, E + int(shared)), dtype=np.float32) * 8 - 4).astype(np.float32)
+    logits[0, 5 % E] = logits[0, 1]                      # exact tie: lower index first
+    S = K + int(shared)
+    ids = dev.empty((T * S + 1,), np.uint32, fill=0x5EADBEEF)
+    sc = dev.empty((T * S + 1,), np.float32, fill=-999.0)
+    backend.moe_router_topk(ids, sc, dev.put(logits), E, K, norm, shared, T)
+    gi, gs = dev.get(ids, np.uint32), dev.get(sc)
+    assert gi[-1] == 0x5EADBEEF and gs[-1] == -999.0     # nothing written past the block
+    ri, rs = oracle_c.router_topk(logits, E, K, norm, shared)
+    assert np.array_equal(gi[:-1].reshape(T, S), ri)
+    assert np.abs(gs[:-1].reshape(T, S) - rs).max() < 2e-6
+    if norm:
+        assert np.abs(gs[:-1].reshape(T, S)[:, :K].sum(1) - 1).max() < 1e-5
+
+
+@pytest.mark.parametrize("T", [1, 3, 16])
+def test_small_block(T, backend, dev, oracle_c):
+    mb = z.synth.moe_block(T, E=16, hidden=256, ffn=128, seed=T)
+    got = run_block(backend, dev, mb, K_top=4)
+    check_block(got, mb, oracle_c, K_top=4)
+    # and against the whole-block numpy restatement (f16 intermediates where the engine stores f16)
+    r = zo.moe_block(mb["x"], mb["logits"], mb["gate"], mb["up"], mb["down"], 16, 4, 128)
+    assert zo.rel_err(got["y"], r["y"].astype(np.float64), 1e-2) <= 5e-3   # real-weights.mjs block bound
+
+
+@pytest.mark.parametrize("T", [1, 16, 256])
+def test_qwen36_class_block(T, backend, dev, oracle_c):
+    """256 experts + shared, hidden 2048, expert ffn 512, top-8, int4 group 64."""
+    mb = z.synth.moe_block(T, seed=0)
+    got = run_block(backend, dev, mb)
+    check_block(got, mb, oracle_c)
+
+
+def test_q3_block(backend, dev, oracle_c):
+    """3-bit experts (int4_matmul_tiled_affine_q3_moe)."""
+    mb = z.synth.moe_block(5, E=32, hidden=512, ffn=256, bits=3, seed=3)
+    got = run_block(backend, dev, mb, K_top=4, bits=3)
+    check_block(got, mb, oracle_c, K_top=4, bits=3)
+
+
+def test_full_size_block_properties(backend, dev, oracle_c):
+    """T = 2048 at full size: routing exact; a sample of (token, slot) pairs against the f64 anchor;
+    and token-permutation invariance (each token's output depends on that token only), bit for bit."""
+    T = 2048
+    mb = z.synth.moe_block(T, seed=0)
+    got = run_block(backend, dev, mb)
+    ids_ref, sc_ref = oracle_c.router_topk(mb["logits"], 256, 8, True, True)
+    assert np.array_equal(got["ids"], ids_ref)
+    sel = np.random.default_rng(1).choice(T, 24, replace=False)
+    sub = dict(mb, T=len(sel), x=mb["x"][sel], logits=mb["logits"][sel])
+    sub_got = {k: v[sel] for k, v in got.items()}
+    check_block(sub_got, sub, oracle_c)
+    perm = np.random.default_rng(2).permutation(T)
+    got_p = run_block(backend, dev, dict(mb, x=mb["x"][perm], logits=mb["logits"][perm]))
+    assert np.array_equal(got_p["y"].view(np.uint16), got["y"][perm].view(np.uint16))
+
+
+def test_bad_expert_id_is_counted_not_followed(backend, dev):
+    """An id outside the stack must not be dereferenced: the pair is skipped and counted."""
+    mb = z.synth.moe_block(2, E=8, hidden=256, ffn=128, seed=1)
+    slots = 3
+    ids = np.array([[0, 99, 8], [1, 2, 3]], dtype=np.uint32)      # 99 is out of range (stack has 9 rows)
+    out = dev.empty((2, slots, 2 * 128), np.float16, fill=7.0)
+    gw, gs, gb = (dev.put(a) for a in mb["gate"])
+    backend.dispatch("int4_matmul_tiled_affine_moe",
+                     [out, dev.put(mb["x"]), gs, gw, moe_gate_pod_args(256, 128, slots), gb, dev.put(ids)],
+                     (32, 2, slots))
+    assert backend.ctx.device_errors() == 1
+    got = dev.get(out)
+    assert (got[0, 1, :128] == 7.0).all()          # skipped pair untouched
+    assert (got[0, 0, :128] != 7.0).any()
+    assert backend.ctx.device_errors() == 0        # counter resets
+
+
+def test_moe_argument_errors(backend, dev):
+    mb = z.synth.moe_block(2, E=8, hidden=256, ffn=128, seed=1)
+    gw, gs, gb = (dev.put(a) for a in mb["gate"])
+    out = dev.empty((2, 3, 256), np.float16)
+    ids = dev.put(np.zeros((2, 3), dtype=np.uint32))
+    x = dev.put(mb["x"])
+    def call(**kw):
+        base = dict(K=256, N=128, M=1, group=64, bits=4, affine=1, out_f32=0, experts=9, slots=3, tokens=2,
+                    in_slot=0, out_slot=256, in_tok=256, out_tok=768, ids_stride=3)
+        base.update(kw)
+        d = z.MoeDesc(z.MmDesc(base["K"], base["N"], base["M"], base["group"], base["bits"], base["affine"],
+                               base["out_f32"]), base["experts"], base["slots"], base["tokens"], base["in_slot"],
+                      base["out_slot"], base["in_tok"], base["out_tok"], base["ids_stride"])
+        backend.ctx.int4_matmul_moe(d, out, x, gs, gw, gb, ids)
+    call()
+    for kw, code in ((dict(affine=0), z.capi.ERR_UNSUPPORTED), (dict(M=4), z.capi.ERR_BAD_DIMS),
+                     (dict(ids_stride=2), z.capi.ERR_BAD_DIMS), (dict(in_tok=252), z.capi.ERR_ALIGNMENT),
+                     (dict(slots=0), z.capi.ERR_BAD_DIMS), (dict(out_f32=1), z.capi.ERR_UNSUPPORTED)):
+        with pytest.raises(z.ZtvmError) as e:
+            call(**kw)
+        assert e.value.status == code, (kw, e.value)
+    call(tokens=0)   # empty token list is a no-op, not an error

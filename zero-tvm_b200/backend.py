@@ -1,0 +1,246 @@
+"""Host-side mirror of the engine's matmul dispatch surface, on top of the C ABI.
+
+The reference selects a WGSL pipeline by ENTRY NAME, binds buffers by slot
+`[out, in, scales, weights, PODArgs, biases?, ids?]` (src/zero-tvm/engine-core.ts:76-92,
+:1699-1703) and records `dispatch(enc, pipeline, bindGroup, wgX, wgY, wgZ, label)`
+(src/zero-tvm/engine-core.ts:2151-2179). `CudaMatmulBackend.dispatch` takes the same things
+and turns them into one call of libztvm_b200.so, so a call site keeps its shape:
+
+    backend.dispatch("int4_matmul_tiled_vec4h_affine", [out, x, scales, weights, pod, biases], grid)
+
+Everything the reference encodes in the entry name (bits, affine, f32 output, MoE) and in
+PODArgs (K_PACKED, SCALES_PER_ROW, N, M_ROWS, MoE strides) is decoded here; the workgroup grid
+only matters for the MoE kernels, where y is the token count and z the slot count.
+"""
+from __future__ import annotations
+
+import re
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+from . import capi
+from .capi import MmDesc, MoeDesc
+
+
+# ---- entry names (src/compiler/shaders/int4_matmul.gen.ts:32-152) ---------------------------
+@dataclass(frozen=True)
+class Int4MatmulOpts:
+    out_f32: bool = False
+    rows_per_wg: int = 1
+    subgroups: bool = False
+    m: int = 1
+    vec4: bool = False
+    vec4_half: bool = False
+    m_dyn: bool = False
+    affine: bool = False
+    moe: bool = False
+    q3: bool = False
+
+
+def int4_matmul_entry(o: Int4MatmulOpts = Int4MatmulOpts()) -> str:
+    """Entry-point name of a variant; same names and same rejections as the reference generator
+    (int4_matmul.gen.ts:137-152 for names, :172-196 for the combinations it refuses)."""
+    if o.moe and not o.affine:
+        raise ValueError("moe requires affine")
+    if o.q3 and not o.affine:
+        raise ValueError("q3 requires affine")
+    if o.affine and o.m != 1:
+        raise ValueError("affine is implemented at m=1 (plus the mDyn path)")
+    if o.q3 and (o.vec4 or o.vec4_half):
+        raise ValueError("q3 has no wide-load path")
+    if o.moe and o.vec4:
+        raise ValueError("moe has no full-vec4 path")
+    if o.rows_per_wg != 1 and not o.subgroups:
+        raise ValueError("rowsPerWG > 1 requires subgroups")
+    if o.m == 4 and (not o.subgroups or o.rows_per_wg != 4):
+        raise ValueError("m=4 requires subgroups + rowsPerWG=4")
+    if o.vec4 and (not o.subgroups or o.m != 1):
+        raise ValueError("vec4 requires subgroups and m=1")
+    if o.vec4_half and (o.vec4 or not o.subgroups or o.m != 1):
+        raise ValueError("vec4Half requires subgroups + m=1 and excludes vec4")
+    if o.m_dyn:
+        if not o.subgroups or o.rows_per_wg != 4 or o.m != 1 or o.vec4 or o.vec4_half or o.out_f32:
+            raise ValueError("mDyn requires subgroups + rowsPerWG=4 (no vec4/outF32/m=4)")
+        return "int4_matmul_batched_dyn_affine" if o.affine else "int4_matmul_batched_dyn"
+    if o.m == 4:
+        return "int4_matmul_batched_m4"
+    name = "int4_matmul"
+    if o.out_f32:
+        name += "_f32"
+    if o.rows_per_wg == 4:
+        name += "_tiled"
+    elif o.rows_per_wg == 8:
+        name += "_tiled8"
+    elif o.subgroups:
+        name += "_sg"
+    if o.vec4:
+        name += "_vec4"
+    elif o.vec4_half:
+        name += "_vec4h"
+    if o.affine:
+        name += "_affine"
+    if o.q3:
+        name += "_q3"
+    if o.moe:
+        name += "_moe"
+    return name
+
+
+# The prefill GEMM generators (int4_matmul.gen.ts:805-1456) and the runtime-M matvec (:580-695).
+_GEMM_ENTRIES = {"int4_matmul_tiled_m", "int4_matmul_tiled_st", "int4_matmul_sgmat", "int4_matmul_sg_e1",
+                 "int4_matmul_sg_e5", "int4_matmul_batched_dyn"}
+_ENTRY_RE = re.compile(r"^int4_matmul(_f32)?(_tiled8|_tiled|_sg)?(_vec4h|_vec4)?(_affine)?(_q3)?(_moe)?$")
+
+
+@dataclass(frozen=True)
+class EntryInfo:
+    affine: bool
+    bits: int
+    out_f32: bool
+    moe: bool
+    has_m_rows: bool      # PODArgs carries M_ROWS (runtime-M kernels)
+    fixed_m: Optional[int]  # batched_m4
+
+
+def parse_entry(entry: str) -> EntryInfo:
+    """Decodes what an entry name fixes. Unknown names raise KeyError, as a missing pipeline does."""
+    if entry == "int4_matmul_batched_m4":
+        return EntryInfo(False, 4, False, False, False, 4)
+    base = entry[:-len("_affine")] if entry.endswith("_affine") else entry
+    if base in _GEMM_ENTRIES:
+        return EntryInfo(entry.endswith("_affine"), 4, False, False, True, None)
+    m = _ENTRY_RE.match(entry)
+    if not m:
+        raise KeyError(f"no such matmul pipeline: {entry}")
+    f32, _rows, _wide, affine, q3, moe = m.groups()
+    if (q3 or moe) and not affine:
+        raise KeyError(f"no such matmul pipeline: {entry}")
+    return EntryInfo(bool(affine), 3 if q3 else 4, bool(f32), bool(moe), False, None)
+
+
+# ---- PODArgs builders (src/zero-tvm/engine-core.ts:787-794, :1021-1022, :1049-1056, :4033-4038) ----
+def pod_args(K: int, N: int, *, bits: int = 4, group: int = 64, m_rows: Optional[int] = None):
+    """[K_PACKED = K*bits/32, SCALES_PER_ROW = K/group, N(, M_ROWS)]."""
+    p = [K * bits // 32, K // group, N]
+    if m_rows is not None:
+        p.append(m_rows)
+    return p
+
+
+def moe_gate_pod_args(d: int, ffn: int, slots: int, bits: int = 4):
+    """gate / up: input shared across slots, output interleaved [slot][2*ffn] (engine-core.ts:1049-1052)."""
+    return [d * bits // 32, d // 64, ffn, 0, 2 * ffn, d, slots * 2 * ffn, slots]
+
+
+def moe_down_pod_args(d: int, ffn: int, slots: int, bits: int = 4):
+    """down: per-slot input [slot][ffn], output [slot][d] (engine-core.ts:1053-1056)."""
+    return [ffn * bits // 32, ffn // 64, d, ffn, d, slots * ffn, slots * d, slots]
+
+
+def moe_slots(top_k: int, has_shared: bool) -> int:
+    """moeSlots = topK + (shared ? 1 : 0) (src/compiler/model-spec.ts:659-660)."""
+    return top_k + (1 if has_shared else 0)
+
+
+# ---- variant resolution (src/zero-tvm/variants.ts:239-320, :370-388) -------------------------------
+def resolve_matmul(*, affine: bool, K: int, out_f32: bool = False, subgroups: bool = True, q3: bool = False,
+                   moe: bool = False) -> str:
+    """The entry name the engine would pick for a decode projection: affine vs symmetric by checkpoint
+    format, the wide-load rung by K divisibility (K%1024 -> vec4 for symmetric, K%512 -> vec4h), 4 rows per
+    workgroup with subgroups. All of them land on the same CUDA GEMV; the name is kept so call sites and
+    logs stay comparable with the reference."""
+    if not subgroups:
+        return int4_matmul_entry(Int4MatmulOpts(out_f32=out_f32, affine=affine, q3=q3))
+    if q3 or (moe and K % 512):
+        return int4_matmul_entry(Int4MatmulOpts(out_f32=out_f32, subgroups=True, rows_per_wg=4, affine=True,
+                                                q3=q3, moe=moe))
+    if affine:
+        return int4_matmul_entry(Int4MatmulOpts(out_f32=out_f32, subgroups=True, rows_per_wg=4,
+                                                vec4_half=(K % 512 == 0), affine=True, moe=moe))
+    return int4_matmul_entry(Int4MatmulOpts(out_f32=out_f32, subgroups=True, rows_per_wg=4,
+                                            vec4=(K % 1024 == 0), vec4_half=(K % 1024 != 0 and K % 512 == 0)))
+
+
+def pick_chunk_gemm(requested: Optional[str], *, affine: bool, K: int) -> str:
+    """Prefill GEMM choice (engine-core.ts:220-245): an explicit request that cannot run throws instead of
+    silently falling back; otherwise the matrix-unit GEMM when K % 64 == 0, else the runtime-M matvec."""
+    suffix = "_affine" if affine else ""
+    names = {"e5": "int4_matmul_sg_e5", "e1": "int4_matmul_sg_e1", "sgmat": "int4_matmul_sgmat",
+             "tiled": "int4_matmul_tiled_st", "matvec": "int4_matmul_batched_dyn"}
+    if requested is not None:
+        if requested not in names:
+            raise ValueError(f"unknown GEMM kernel '{requested}'")
+        if requested != "matvec" and K % 64:
+            raise ValueError(f"GEMM kernel '{requested}' needs K % 64 == 0 (K={K})")
+        return names[requested] + suffix
+    return (names["e5"] if K % 64 == 0 else names["matvec"]) + suffix
+
+
+# ---- the dispatch surface ---------------------------------------------------------------------------
+class CudaMatmulBackend:
+    """Drop-in for the matmul entries of compile() + dispatch(): one object per GPU."""
+
+    def __init__(self, device: int = 0):
+        self.ctx = capi.Context(device)
+
+    def close(self):
+        self.ctx.close()
+
+    def dispatch(self, entry: str, bindings: Sequence, grid: Sequence[int] = (1, 1, 1), stream=None):
+        """bindings = [out, in, scales, weights, PODArgs, biases?, ids?] in bind-group slot order;
+        PODArgs is the list of u32 the engine writes into the uniform buffer."""
+        info = parse_entry(entry)
+        if len(bindings) < 5:
+            raise ValueError("bind group needs [out, in, scales, weights, PODArgs, ...]")
+        out, x, scales, weights, pod = bindings[:5]
+        biases = bindings[5] if len(bindings) > 5 else None
+        ids = bindings[6] if len(bindings) > 6 else None
+        if info.affine and biases is None:
+            raise ValueError(f"{entry}: affine variants bind biases at slot 5")
+        k_packed, spr, n = int(pod[0]), int(pod[1]), int(pod[2])
+        if k_packed <= 0 or spr <= 0 or (k_packed * 32) % info.bits:
+            raise ValueError(f"{entry}: bad PODArgs {list(pod)}")
+        K = k_packed * 32 // info.bits
+        group = K // spr
+        if info.moe:
+            if len(pod) < 8 or ids is None:
+                raise ValueError(f"{entry}: MoE variants need 8 PODArgs fields and ids at slot 6")
+            gx, gy, gz = (list(grid) + [1, 1, 1])[:3]
+            desc = MoeDesc(MmDesc(K, n, 1, group, info.bits, 1, 0), 0, gz, gy, int(pod[3]), int(pod[4]),
+                           int(pod[5]), int(pod[6]), int(pod[7]))
+            desc.experts = self._experts_of(weights, n, k_packed)
+            self.ctx.int4_matmul_moe(desc, out, x, scales, weights, biases, ids, stream)
+            return
+        if info.fixed_m is not None:
+            M = info.fixed_m
+        elif info.has_m_rows:
+            if len(pod) < 4:
+                raise ValueError(f"{entry}: runtime-M kernels read M_ROWS from PODArgs[3]")
+            M = int(pod[3])
+            if M == 0:
+                return
+        else:
+            M = 1
+        desc = MmDesc(K, n, M, group, info.bits, int(info.affine), int(info.out_f32))
+        self.ctx.int4_matmul(desc, out, x, scales, weights, biases if info.affine else None, stream)
+
+    @staticmethod
+    def _experts_of(weights, n: int, k_packed: int) -> int:
+        """Rows of the expert stack, from the bound buffer's size (the reference relies on WebGPU's
+        bounds checks; here an out-of-range id is counted and skipped, so the count must be known)."""
+        if hasattr(weights, "numel"):
+            return int(weights.numel() * weights.element_size() // (4 * n * k_packed))
+        if hasattr(weights, "nbytes"):
+            return int(weights.nbytes // (4 * n * k_packed))
+        raise TypeError("MoE weights must be a sized buffer (tensor / array) so the expert count is known")
+
+    # MoE glue, same argument order as the reference bind groups
+    def moe_router_topk(self, ids, scores, logits, E: int, K: int, norm_topk: bool, has_shared: bool, tokens: int,
+                        stream=None):
+        self.ctx.moe_route_topk(E, K, norm_topk, has_shared, tokens, ids, scores, logits, stream)
+
+    def silu_mul(self, out, gate_up, rows: int, ffn: int, stream=None):
+        self.ctx.silu_mul(rows, ffn, out, gate_up, stream)
+
+    def moe_combine(self, out, y_slots, scores, tokens: int, slots: int, d: int, stream=None):
+        self.ctx.moe_combine(tokens, slots, d, out, y_slots, scores, stream)

@@ -1,0 +1,164 @@
+"""ctypes binding of libztvm_b200.so — the same C ABI a Node-API addon would bind.
+
+There is no fallback: if the shared library is missing or a call fails, an exception carries the
+library's own message. Buffers are raw device addresses (ints) or any object with `data_ptr()`.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libztvm_b200.so")
+
+# every symbol include/ztvm_b200.h declares
+SYMBOLS = [
+    "ztvm_version", "ztvm_status_string", "ztvm_init", "ztvm_destroy", "ztvm_last_error", "ztvm_sync",
+    "ztvm_int4_matmul", "ztvm_int4_matmul_host", "ztvm_int4_matmul_moe", "ztvm_moe_route_topk", "ztvm_silu_mul",
+    "ztvm_moe_combine", "ztvm_unpack_codes", "ztvm_dequant", "ztvm_device_errors",
+]
+
+OK, ERR_NULL_POINTER, ERR_BAD_DIMS, ERR_UNSUPPORTED, ERR_ALIGNMENT, ERR_CUDA, ERR_BAD_CONTEXT, ERR_TOO_LARGE = range(8)
+
+
+class ZtvmError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"ztvm status {status}: {message}")
+        self.status = status
+
+
+class MmDesc(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("K", "N", "M", "group", "bits", "affine", "out_f32")]
+
+
+class MoeDesc(C.Structure):
+    _fields_ = [("mm", MmDesc)] + [(n, C.c_uint32) for n in (
+        "experts", "slots", "tokens", "in_slot_stride", "out_slot_stride", "in_tok_stride", "out_tok_stride",
+        "ids_stride")]
+
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Loads the library; raises if it has not been built (no CPU path exists)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ZtvmError(-1, f"{LIB_PATH} is missing: build it with `python zero-tvm_b200/build.py` "
+                            "(CUDA sm_100a only; this package has no CPU implementation)")
+    lib = C.CDLL(LIB_PATH)
+    vp, u32, i32 = C.c_void_p, C.c_uint32, C.c_int32
+    lib.ztvm_version.restype = i32
+    lib.ztvm_status_string.restype = C.c_char_p
+    lib.ztvm_status_string.argtypes = [i32]
+    lib.ztvm_last_error.restype = C.c_char_p
+    lib.ztvm_last_error.argtypes = [vp]
+    sig = {
+        "ztvm_init": [i32, C.POINTER(vp)],
+        "ztvm_destroy": [vp],
+        "ztvm_sync": [vp],
+        "ztvm_int4_matmul": [vp, C.POINTER(MmDesc), vp, vp, vp, vp, vp, vp],
+        "ztvm_int4_matmul_host": [vp, C.POINTER(MmDesc), vp, vp, vp, vp, vp],
+        "ztvm_int4_matmul_moe": [vp, C.POINTER(MoeDesc), vp, vp, vp, vp, vp, vp, vp],
+        "ztvm_moe_route_topk": [vp, u32, u32, u32, u32, u32, vp, vp, vp, vp],
+        "ztvm_silu_mul": [vp, u32, u32, vp, vp, vp],
+        "ztvm_moe_combine": [vp, u32, u32, u32, vp, vp, vp, vp],
+        "ztvm_unpack_codes": [vp, C.POINTER(MmDesc), vp, vp, vp],
+        "ztvm_dequant": [vp, C.POINTER(MmDesc), vp, i32, vp, vp, vp, vp],
+        "ztvm_device_errors": [vp, vp, C.POINTER(u32)],
+    }
+    for name, args in sig.items():
+        fn = getattr(lib, name)
+        fn.restype = i32
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def ptr(buf):
+    """Device (or host) address of `buf`: None, int, or an object with data_ptr() / ctypes data."""
+    if buf is None:
+        return None
+    if isinstance(buf, int):
+        return C.c_void_p(buf)
+    if hasattr(buf, "data_ptr"):
+        return C.c_void_p(buf.data_ptr())
+    if hasattr(buf, "ctypes"):
+        return C.c_void_p(buf.ctypes.data)
+    raise TypeError(f"cannot take the address of {type(buf)!r}")
+
+
+def stream_ptr(stream):
+    if stream is None:
+        return None
+    if isinstance(stream, int):
+        return C.c_void_p(stream)
+    return C.c_void_p(stream.cuda_stream)  # torch.cuda.Stream
+
+
+def check(status: int):
+    if status != OK:
+        raise ZtvmError(status, load().ztvm_last_error(None).decode())
+
+
+class Context:
+    """One per GPU; owns the library context (stream, staging, error counter)."""
+
+    def __init__(self, device: int = 0):
+        self._lib = load()
+        h = C.c_void_p()
+        check(self._lib.ztvm_init(device, C.byref(h)))
+        self.handle = h
+        self.device = device
+
+    def close(self):
+        if getattr(self, "handle", None):
+            check(self._lib.ztvm_destroy(self.handle))
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def sync(self):
+        check(self._lib.ztvm_sync(self.handle))
+
+    # -- entry points, thin and literal --------------------------------------------------------
+    def int4_matmul(self, desc: MmDesc, y, x, scales, packed_w, biases=None, stream=None):
+        check(self._lib.ztvm_int4_matmul(self.handle, C.byref(desc), ptr(y), ptr(x), ptr(scales), ptr(packed_w),
+                                         ptr(biases), stream_ptr(stream)))
+
+    def int4_matmul_host(self, desc: MmDesc, y_host, x_host, scales, packed_w, biases=None):
+        check(self._lib.ztvm_int4_matmul_host(self.handle, C.byref(desc), ptr(y_host), ptr(x_host), ptr(scales),
+                                              ptr(packed_w), ptr(biases)))
+
+    def int4_matmul_moe(self, desc: MoeDesc, y, x, scales, packed_w, biases, ids, stream=None):
+        check(self._lib.ztvm_int4_matmul_moe(self.handle, C.byref(desc), ptr(y), ptr(x), ptr(scales),
+                                             ptr(packed_w), ptr(biases), ptr(ids), stream_ptr(stream)))
+
+    def moe_route_topk(self, E, K, norm_topk, has_shared, tokens, ids, scores, logits, stream=None):
+        check(self._lib.ztvm_moe_route_topk(self.handle, E, K, int(norm_topk), int(has_shared), tokens, ptr(ids),
+                                            ptr(scores), ptr(logits), stream_ptr(stream)))
+
+    def silu_mul(self, rows, ffn, h, gate_up, stream=None):
+        check(self._lib.ztvm_silu_mul(self.handle, rows, ffn, ptr(h), ptr(gate_up), stream_ptr(stream)))
+
+    def moe_combine(self, tokens, slots, d, out, y_slots, scores, stream=None):
+        check(self._lib.ztvm_moe_combine(self.handle, tokens, slots, d, ptr(out), ptr(y_slots), ptr(scores),
+                                         stream_ptr(stream)))
+
+    def unpack_codes(self, desc: MmDesc, codes, packed_w, stream=None):
+        check(self._lib.ztvm_unpack_codes(self.handle, C.byref(desc), ptr(codes), ptr(packed_w), stream_ptr(stream)))
+
+    def dequant(self, desc: MmDesc, w_out, as_f16, scales, packed_w, biases=None, stream=None):
+        check(self._lib.ztvm_dequant(self.handle, C.byref(desc), ptr(w_out), int(as_f16), ptr(scales),
+                                     ptr(packed_w), ptr(biases), stream_ptr(stream)))
+
+    def device_errors(self, stream=None) -> int:
+        n = C.c_uint32(0)
+        check(self._lib.ztvm_device_errors(self.handle, stream_ptr(stream), C.byref(n)))
+        return n.value

@@ -1,0 +1,345 @@
+// C ABI of libztvm_b200.so: context, argument validation, kernel selection. Every entry point
+// validates before it launches and reports through a status code plus a thread-local message.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "../../include/ztvm_b200.h"
+#include "ztvm_kernels.h"
+
+struct ztvm_ctx {
+  uint32_t magic;
+  int device;
+  int sm_count;
+  cudaStream_t stream;
+  uint32_t* err_counter;  // device word: out-of-range expert ids seen by the MoE kernels
+  // staging for the host-buffer entry point (grown on demand, freed at destroy)
+  void* h_pinned; size_t h_pinned_bytes;
+  void* d_x; size_t d_x_bytes;
+  void* d_y; size_t d_y_bytes;
+};
+
+namespace {
+
+constexpr uint32_t kMagic = 0x5a54564du;  // "ZTVM"
+thread_local char g_err[512] = "";
+
+ztvm_status fail(ztvm_status s, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return s;
+}
+ztvm_status cuda_fail(cudaError_t e, const char* what) {
+  return fail(ZTVM_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+#define ZTVM_CUDA(call)                                      \
+  do {                                                       \
+    cudaError_t e_ = (call);                                 \
+    if (e_ != cudaSuccess) return cuda_fail(e_, #call);      \
+  } while (0)
+
+ztvm_status check_ctx(ztvm_ctx* ctx) {
+  if (!ctx) return fail(ZTVM_ERR_BAD_CONTEXT, "context is NULL");
+  if (ctx->magic != kMagic) return fail(ZTVM_ERR_BAD_CONTEXT, "context is not live (destroyed or corrupt)");
+  int dev = -1;
+  ZTVM_CUDA(cudaGetDevice(&dev));
+  if (dev != ctx->device) ZTVM_CUDA(cudaSetDevice(ctx->device));
+  return ZTVM_OK;
+}
+
+bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+int log2_exact(uint32_t v) {
+  if (v == 0 || (v & (v - 1))) return -1;
+  int s = 0;
+  while ((1u << s) != v) ++s;
+  return s;
+}
+
+// Layout rules shared by every matmul entry point.
+ztvm_status check_desc(const ztvm_mm_desc* d, bool need_m) {
+  if (!d) return fail(ZTVM_ERR_NULL_POINTER, "desc is NULL");
+  if (d->bits != 4 && d->bits != 3) return fail(ZTVM_ERR_UNSUPPORTED, "bits=%u: only 4 and 3 are implemented", d->bits);
+  if (d->bits == 3 && !d->affine)
+    return fail(ZTVM_ERR_UNSUPPORTED, "3-bit weights exist only in the affine layout");
+  const int gs = log2_exact(d->group);
+  if (gs < 5 || gs > 8) return fail(ZTVM_ERR_BAD_DIMS, "group=%u: must be a power of two in [32, 256]", d->group);
+  if (d->K == 0 || d->N == 0) return fail(ZTVM_ERR_BAD_DIMS, "K=%u N=%u: must be non-zero", d->K, d->N);
+  if (d->K % d->group) return fail(ZTVM_ERR_BAD_DIMS, "K=%u is not a multiple of group=%u", d->K, d->group);
+  if (need_m && d->M == 0) return fail(ZTVM_ERR_BAD_DIMS, "M=0");
+  if ((uint64_t)d->N * (d->K / 32 * d->bits) > 0xFFFFFFFFull * 4ull)
+    return fail(ZTVM_ERR_TOO_LARGE, "N*K too large");
+  return ZTVM_OK;
+}
+
+ztvm::GemvParams gemv_params(const ztvm_mm_desc* d, void* y, const void* x, const void* s, const void* w,
+                             const void* b) {
+  ztvm::GemvParams p;
+  memset(&p, 0, sizeof(p));
+  p.W = static_cast<const uint32_t*>(w);
+  p.S = static_cast<const __half*>(s);
+  p.B = d->affine ? static_cast<const __half*>(b) : nullptr;
+  p.X = static_cast<const __half*>(x);
+  p.Y = y;
+  p.K = d->K; p.N = d->N; p.M = d->M;
+  p.KP = d->K / 32 * d->bits;
+  p.SPR = d->K / d->group;
+  p.group_shift = (uint32_t)log2_exact(d->group);
+  p.out_f32 = d->out_f32 ? 1u : 0u;
+  p.x_row_stride = d->K;
+  p.y_row_stride = d->N;
+  return p;
+}
+
+ztvm_status check_buffers(const ztvm_mm_desc* d, const void* y, const void* x, const void* s, const void* w,
+                          const void* b) {
+  if (!y || !x || !s || !w) return fail(ZTVM_ERR_NULL_POINTER, "y/x/scales/packed_w must be non-NULL");
+  if (d->affine && !b) return fail(ZTVM_ERR_NULL_POINTER, "affine weights need biases");
+  if (!aligned(w, 16) || !aligned(x, 16)) return fail(ZTVM_ERR_ALIGNMENT, "packed_w and x must be 16-byte aligned");
+  if (!aligned(s, 2) || (b && !aligned(b, 2)) || !aligned(y, d->out_f32 ? 4 : 2))
+    return fail(ZTVM_ERR_ALIGNMENT, "scales/biases/y are misaligned for their element type");
+  return ZTVM_OK;
+}
+
+ztvm_status grow(void** p, size_t* have, size_t need, bool pinned) {
+  if (*have >= need) return ZTVM_OK;
+  if (*p) {
+    if (pinned) ZTVM_CUDA(cudaFreeHost(*p)); else ZTVM_CUDA(cudaFree(*p));
+    *p = nullptr; *have = 0;
+  }
+  size_t cap = need + need / 2;
+  if (pinned) ZTVM_CUDA(cudaMallocHost(p, cap)); else ZTVM_CUDA(cudaMalloc(p, cap));
+  *have = cap;
+  return ZTVM_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t ztvm_version(void) { return 100; }
+
+const char* ztvm_status_string(ztvm_status s) {
+  switch (s) {
+    case ZTVM_OK: return "ok";
+    case ZTVM_ERR_NULL_POINTER: return "null pointer";
+    case ZTVM_ERR_BAD_DIMS: return "bad dimensions";
+    case ZTVM_ERR_UNSUPPORTED: return "unsupported combination";
+    case ZTVM_ERR_ALIGNMENT: return "misaligned buffer";
+    case ZTVM_ERR_CUDA: return "CUDA error";
+    case ZTVM_ERR_BAD_CONTEXT: return "bad context";
+    case ZTVM_ERR_TOO_LARGE: return "size beyond limit";
+    default: return "unknown status";
+  }
+}
+
+const char* ztvm_last_error(ztvm_ctx*) { return g_err; }
+
+ztvm_status ztvm_init(int32_t device_ordinal, ztvm_ctx** out_ctx) {
+  if (!out_ctx) return fail(ZTVM_ERR_NULL_POINTER, "out_ctx is NULL");
+  *out_ctx = nullptr;
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDeviceCount (no usable CUDA device: this library has no CPU path)");
+  if (device_ordinal < 0 || device_ordinal >= count)
+    return fail(ZTVM_ERR_BAD_CONTEXT, "device %d out of range (%d devices)", device_ordinal, count);
+  ZTVM_CUDA(cudaSetDevice(device_ordinal));
+  cudaDeviceProp prop;
+  ZTVM_CUDA(cudaGetDeviceProperties(&prop, device_ordinal));
+  if (prop.major != 10)
+    return fail(ZTVM_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library is built for sm_100a only", device_ordinal,
+                prop.major, prop.minor);
+  ztvm_ctx* c = new (std::nothrow) ztvm_ctx();
+  if (!c) return fail(ZTVM_ERR_CUDA, "out of host memory");
+  memset(c, 0, sizeof(*c));
+  c->device = device_ordinal;
+  c->sm_count = prop.multiProcessorCount;
+  e = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&c->err_counter), 256);
+  if (e == cudaSuccess) e = cudaMemset(c->err_counter, 0, 256);
+  if (e != cudaSuccess) {
+    if (c->stream) cudaStreamDestroy(c->stream);
+    delete c;
+    return cuda_fail(e, "context set-up");
+  }
+  c->magic = kMagic;
+  *out_ctx = c;
+  return ZTVM_OK;
+}
+
+ztvm_status ztvm_destroy(ztvm_ctx* ctx) {
+  ztvm_status s = check_ctx(ctx);
+  if (s) return s;
+  cudaStreamSynchronize(ctx->stream);
+  if (ctx->h_pinned) cudaFreeHost(ctx->h_pinned);
+  if (ctx->d_x) cudaFree(ctx->d_x);
+  if (ctx->d_y) cudaFree(ctx->d_y);
+  cudaFree(ctx->err_counter);
+  cudaStreamDestroy(ctx->stream);
+  ctx->magic = 0;
+  delete ctx;
+  return ZTVM_OK;
+}
+
+ztvm_status ztvm_sync(ztvm_ctx* ctx) {
+  ztvm_status s = check_ctx(ctx);
+  if (s) return s;
+  ZTVM_CUDA(cudaStreamSynchronize(ctx->stream));
+  return ZTVM_OK;
+}
+
+ztvm_status ztvm_int4_matmul(ztvm_ctx* ctx, const ztvm_mm_desc* d, void* y, const void* x, const void* scales,
+                             const void* packed_w, const void* biases, void* stream) {
+  ztvm_status s = check_ctx(ctx);
+  if (s) return s;
+  if ((s = check_desc(d, true))) return s;
+  if ((s = check_buffers(d, y, x, scales, packed_w, biases))) return s;
+  cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : ctx->stream;
+  // Rows are processed in slabs of at most 8 by the GEMV.
+  for (uint32_t m0 = 0; m0 < d->M; m0 += 8) {
+    ztvm_mm_desc dd = *d;
+    dd.M = d->M - m0 < 8 ? d->M - m0 : 8;
+    ztvm::GemvParams p = gemv_params(&dd, y, x, scales, packed_w, biases);
+    p.X = static_cast<const __half*>(x) + (size_t)m0 * d->K;
+    p.Y = d->out_f32 ? static_cast<void*>(static_cast<float*>(y) + (size_t)m0 * d->N)
+                     : static_cast<void*>(static_cast<__half*>(y) + (size_t)m0 * d->N);
+    ZTVM_CUDA(ztvm::launch_gemv(p, (int)d->bits, false, 1, 1, ctx->sm_count, st));
+  }
+  return ZTVM_OK;
+}
+
+ztvm_status ztvm_int4_matmul_host(ztvm_ctx* ctx, const ztvm_mm_desc* d, void* y_host, const void* x_host,
+                                  const void* scales, const void* packed_w, const void* biases) {
+  ztvm_status s = check_ctx(ctx);
+  if (s) return s;
+  if ((s = check_desc(d, true))) return s;
+  if (!y_host || !x_host) return fail(ZTVM_ERR_NULL_POINTER, "y_host/x_host must be non-NULL");
+  const size_t xb = (size_t)d->M * d->K * 2, yb = (size_t)d->M * d->N * (d->out_f32 ? 4 : 2);
+  if ((s = grow(&ctx->h_pinned, &ctx->h_pinned_bytes, xb + yb, true))) return s;
+  if ((s = grow(&ctx->d_x, &ctx->d_x_bytes, xb, false))) return s;
+  if ((s = grow(&ctx->d_y, &ctx->d_y_bytes, yb, false))) return s;
+  char* hp = static_cast<char*>(ctx->h_pinned);
+  memcpy(hp, x_host, xb);
+  ZTVM_CUDA(cudaMemcpyAsync(ctx->d_x, hp, xb, cudaMemcpyHostToDevice, ctx->stream));
+  if ((s = ztvm_int4_matmul(ctx, d, ctx->d_y, ctx->d_x, scales, packed_w, biases, ctx->stream))) return s;
+  ZTVM_CUDA(cudaMemcpyAsync(hp + xb, ctx->d_y, yb, cudaMemcpyDeviceToHost, ctx->stream));
+  ZTVM_CUDA(cudaStreamSynchronize(ctx->stream));
+  memcpy(y_host, hp + xb, yb);
+  return ZTVM_OK;
+}
+
+ztvm_status ztvm_int4_matmul_moe(ztvm_ctx* ctx, const ztvm_moe_desc* md, void* y, const void* x, const void* scales,
+                                 const void* packed_w, const void* biases, const uint32_t* ids, void* stream) {
+  ztvm_status s = check_ctx(ctx);
+  if (s) return s;
+  if (!md) return fail(ZTVM_ERR_NULL_POINTER, "desc is NULL");
+  const ztvm_mm_desc* d = &md->mm;
+  if ((s = check_desc(d, false))) return s;
+  if (!d->affine) return fail(ZTVM_ERR_UNSUPPORTED, "MoE expert weights are affine-quantised only");
+  if (d->out_f32) return fail(ZTVM_ERR_UNSUPPORTED, "MoE expert matmuls write f16");
+  if (d->M > 1) return fail(ZTVM_ERR_BAD_DIMS, "MoE matmul is per (token, slot): mm.M must be 1 (or 0)");
+  if ((s = check_buffers(d, y, x, scales, packed_w, biases))) return s;
+  if (!ids) return fail(ZTVM_ERR_NULL_POINTER, "ids is NULL");
+  if (md->tokens == 0) return ZTVM_OK;
+  if (md->slots == 0 || md->experts == 0) return fail(ZTVM_ERR_BAD_DIMS, "slots and experts must be non-zero");
+  if (md->slots > 65535) return fail(ZTVM_ERR_TOO_LARGE, "slots=%u exceeds 65535", md->slots);
+  if (md->ids_stride < md->slots) return fail(ZTVM_ERR_BAD_DIMS, "ids_stride=%u < slots=%u", md->ids_stride, md->slots);
+  if ((md->in_slot_stride | md->in_tok_stride) % 8)
+    return fail(ZTVM_ERR_ALIGNMENT, "input strides must be multiples of 8 elements (16-byte activation loads)");
+  cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : ctx->stream;
+  ztvm_mm_desc dd = *d;
+  dd.M = 1;
+  // grid.y carries the token: split very long token lists into slabs of 65535
+  for (uint32_t t0 = 0; t0 < md->tokens; t0 += 65535) {
+    const uint32_t nt = md->tokens - t0 < 65535 ? md->tokens - t0 : 65535;
+    ztvm::GemvParams p = gemv_params(&dd, y, x, scales, packed_w, biases);
+    p.X = static_cast<const __half*>(x) + (size_t)t0 * md->in_tok_stride;
+    p.Y = static_cast<__half*>(y) + (size_t)t0 * md->out_tok_stride;
+    p.ids = ids + (size_t)t0 * md->ids_stride;
+    p.experts = md->experts;
+    p.in_slot_stride = md->in_slot_stride; p.out_slot_stride = md->out_slot_stride;
+    p.in_tok_stride = md->in_tok_stride; p.out_tok_stride = md->out_tok_stride;
+    p.ids_stride = md->ids_stride;
+    p.err_counter = ctx->err_counter;
+    ZTVM_CUDA(ztvm::launch_gemv(p, (int)d->bits, true, nt, md->slots, ctx->sm_count, st));
+  }
+  return ZTVM_OK;
+}
+
+ztvm_status ztvm_moe_route_topk(ztvm_ctx* ctx, uint32_t E, uint32_t K, uint32_t norm_topk, uint32_t has_shared,
+                                uint32_t tokens, uint32_t* ids, float* scores, const float* logits, void* stream) {
+  ztvm_status s = check_ctx(ctx);
+  if (s) return s;
+  if (!ids || !scores || !logits) return fail(ZTVM_ERR_NULL_POINTER, "ids/scores/logits must be non-NULL");
+  if (E == 0 || E > 1024) return fail(ZTVM_ERR_TOO_LARGE, "E=%u: 1..1024 routed experts supported", E);
+  if (K == 0 || K > 32 || K > E) return fail(ZTVM_ERR_BAD_DIMS, "K=%u: need 1 <= K <= min(32, E)", K);
+  if (tokens == 0) return ZTVM_OK;
+  cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : ctx->stream;
+  ZTVM_CUDA(ztvm::launch_route_topk(logits, ids, scores, tokens, E, K, norm_topk != 0, has_shared != 0, st));
+  return ZTVM_OK;
+}
+
+ztvm_status ztvm_silu_mul(ztvm_ctx* ctx, uint32_t rows, uint32_t ffn, void* h, const void* gate_up, void* stream) {
+  ztvm_status s = check_ctx(ctx);
+  if (s) return s;
+  if (!h || !gate_up) return fail(ZTVM_ERR_NULL_POINTER, "h/gate_up must be non-NULL");
+  if (ffn == 0) return fail(ZTVM_ERR_BAD_DIMS, "ffn=0");
+  cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : ctx->stream;
+  ZTVM_CUDA(ztvm::launch_silu_mul(static_cast<const __half*>(gate_up), static_cast<__half*>(h), rows, ffn, st));
+  return ZTVM_OK;
+}
+
+ztvm_status ztvm_moe_combine(ztvm_ctx* ctx, uint32_t tokens, uint32_t slots, uint32_t d, void* out,
+                             const void* y_slots, const float* scores, void* stream) {
+  ztvm_status s = check_ctx(ctx);
+  if (s) return s;
+  if (!out || !y_slots || !scores) return fail(ZTVM_ERR_NULL_POINTER, "out/y_slots/scores must be non-NULL");
+  if (slots == 0 || d == 0) return fail(ZTVM_ERR_BAD_DIMS, "slots and d must be non-zero");
+  cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : ctx->stream;
+  ZTVM_CUDA(ztvm::launch_moe_combine(static_cast<const __half*>(y_slots), scores, static_cast<__half*>(out), tokens,
+                                     slots, d, st));
+  return ZTVM_OK;
+}
+
+ztvm_status ztvm_unpack_codes(ztvm_ctx* ctx, const ztvm_mm_desc* d, uint8_t* codes, const void* packed_w,
+                              void* stream) {
+  ztvm_status s = check_ctx(ctx);
+  if (s) return s;
+  if ((s = check_desc(d, false))) return s;
+  if (!codes || !packed_w) return fail(ZTVM_ERR_NULL_POINTER, "codes/packed_w must be non-NULL");
+  if (!aligned(codes, 8) || !aligned(packed_w, 4)) return fail(ZTVM_ERR_ALIGNMENT, "codes need 8-byte alignment");
+  cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : ctx->stream;
+  ZTVM_CUDA(ztvm::launch_unpack_codes(static_cast<const uint32_t*>(packed_w), codes, d->N, d->K, (int)d->bits, st));
+  return ZTVM_OK;
+}
+
+ztvm_status ztvm_dequant(ztvm_ctx* ctx, const ztvm_mm_desc* d, void* w_out, int32_t as_f16, const void* scales,
+                         const void* packed_w, const void* biases, void* stream) {
+  ztvm_status s = check_ctx(ctx);
+  if (s) return s;
+  if ((s = check_desc(d, false))) return s;
+  if (!w_out || !packed_w || !scales) return fail(ZTVM_ERR_NULL_POINTER, "w_out/scales/packed_w must be non-NULL");
+  if (d->affine && !biases) return fail(ZTVM_ERR_NULL_POINTER, "affine weights need biases");
+  if (!aligned(w_out, 16)) return fail(ZTVM_ERR_ALIGNMENT, "w_out needs 16-byte alignment");
+  cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : ctx->stream;
+  ZTVM_CUDA(ztvm::launch_dequant(static_cast<const uint32_t*>(packed_w), static_cast<const __half*>(scales),
+                                 static_cast<const __half*>(biases), w_out, d->N, d->K, (int)d->bits,
+                                 (uint32_t)log2_exact(d->group), d->affine != 0, as_f16 != 0, st));
+  return ZTVM_OK;
+}
+
+ztvm_status ztvm_device_errors(ztvm_ctx* ctx, void* stream, uint32_t* count) {
+  ztvm_status s = check_ctx(ctx);
+  if (s) return s;
+  if (!count) return fail(ZTVM_ERR_NULL_POINTER, "count is NULL");
+  if (stream) ZTVM_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  ZTVM_CUDA(cudaStreamSynchronize(ctx->stream));
+  ZTVM_CUDA(cudaMemcpy(count, ctx->err_counter, 4, cudaMemcpyDeviceToHost));
+  ZTVM_CUDA(cudaMemset(ctx->err_counter, 0, 4));
+  return ZTVM_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,217 @@
+// Parity hooks (unpack / dequant) and the MoE glue kernels around the expert matmuls:
+// router top-k, SiLU*up, weighted combine.
+#include "ztvm_device.cuh"
+#include "ztvm_kernels.h"
+
+namespace ztvm {
+
+// ---- parity hooks ------------------------------------------------------------------------------
+// One thread per 8-code block. 4-bit: block = one word. 3-bit: block j of a 32-code unit is the
+// 24-bit window at bit 24j of the unit's three words.
+template <int BITS>
+__device__ __forceinline__ void load_block_codes(const uint32_t* W, uint32_t KP, uint32_t n, uint32_t blk, float q[8]) {
+  const uint32_t* row = W + (size_t)n * KP;
+  if constexpr (BITS == 4) {
+    codes4_f32(row[blk], q);
+  } else {
+    const uint32_t u = blk >> 2, j = blk & 3;
+    const uint32_t w0 = row[u * 3], w1 = row[u * 3 + 1], w2 = row[u * 3 + 2];
+    uint32_t win;
+    switch (j) {
+      case 0: win = window3(w0, w1, w2, 0); break;
+      case 1: win = window3(w0, w1, w2, 1); break;
+      case 2: win = window3(w0, w1, w2, 2); break;
+      default: win = window3(w0, w1, w2, 3); break;
+    }
+    codes3_f32(win, q);
+  }
+}
+
+template <int BITS>
+__global__ void unpack_codes_kernel(const uint32_t* W, uint8_t* codes, uint32_t N, uint32_t K) {
+  const uint32_t nblk = K >> 3, KP = K * BITS / 32;
+  const size_t total = (size_t)N * nblk;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const uint32_t n = (uint32_t)(i / nblk), blk = (uint32_t)(i - (size_t)n * nblk);
+    float q[8];
+    load_block_codes<BITS>(W, KP, n, blk, q);
+    uint2 o;
+    o.x = (uint32_t)q[0] | ((uint32_t)q[1] << 8) | ((uint32_t)q[2] << 16) | ((uint32_t)q[3] << 24);
+    o.y = (uint32_t)q[4] | ((uint32_t)q[5] << 8) | ((uint32_t)q[6] << 16) | ((uint32_t)q[7] << 24);
+    *reinterpret_cast<uint2*>(codes + i * 8) = o;
+  }
+}
+
+template <int BITS, bool AFFINE, bool AS_F16>
+__global__ void dequant_kernel(const uint32_t* W, const __half* S, const __half* B, void* out, uint32_t N, uint32_t K,
+                               uint32_t group_shift) {
+  const uint32_t nblk = K >> 3, KP = K * BITS / 32, SPR = K >> group_shift;
+  const size_t total = (size_t)N * nblk;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const uint32_t n = (uint32_t)(i / nblk), blk = (uint32_t)(i - (size_t)n * nblk);
+    float q[8];
+    load_block_codes<BITS>(W, KP, n, blk, q);
+    const uint32_t g = (blk << 3) >> group_shift;
+    const float s = __half2float(S[(size_t)n * SPR + g]);
+    const float b = AFFINE ? __half2float(B[(size_t)n * SPR + g]) : 0.f;
+    if constexpr (AS_F16) {
+      __half h[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) h[k] = dequant_w16<AFFINE>(q[k], s, b);
+      *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(out) + i * 8) = *reinterpret_cast<uint4*>(h);
+    } else {
+      float4 lo, hi;
+      lo.x = dequant_w32<AFFINE>(q[0], s, b); lo.y = dequant_w32<AFFINE>(q[1], s, b);
+      lo.z = dequant_w32<AFFINE>(q[2], s, b); lo.w = dequant_w32<AFFINE>(q[3], s, b);
+      hi.x = dequant_w32<AFFINE>(q[4], s, b); hi.y = dequant_w32<AFFINE>(q[5], s, b);
+      hi.z = dequant_w32<AFFINE>(q[6], s, b); hi.w = dequant_w32<AFFINE>(q[7], s, b);
+      float4* o = reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + i * 8);
+      o[0] = lo; o[1] = hi;
+    }
+  }
+}
+
+static inline unsigned grid_for(size_t total, int block) {
+  size_t g = (total + block - 1) / block;
+  return (unsigned)(g > 148 * 32 ? 148 * 32 : (g ? g : 1));
+}
+
+cudaError_t launch_unpack_codes(const uint32_t* W, uint8_t* codes, uint32_t N, uint32_t K, int bits, cudaStream_t st) {
+  const size_t total = (size_t)N * (K >> 3);
+  if (bits == 4) unpack_codes_kernel<4><<<grid_for(total, 256), 256, 0, st>>>(W, codes, N, K);
+  else unpack_codes_kernel<3><<<grid_for(total, 256), 256, 0, st>>>(W, codes, N, K);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_dequant(const uint32_t* W, const __half* S, const __half* B, void* out, uint32_t N, uint32_t K,
+                           int bits, uint32_t group_shift, bool affine, bool as_f16, cudaStream_t st) {
+  const size_t total = (size_t)N * (K >> 3);
+  const unsigned g = grid_for(total, 256);
+#define ZTVM_DQ(BITS_, AFF_, F16_) dequant_kernel<BITS_, AFF_, F16_><<<g, 256, 0, st>>>(W, S, B, out, N, K, group_shift)
+  if (bits == 4) {
+    if (affine) { if (as_f16) ZTVM_DQ(4, true, true); else ZTVM_DQ(4, true, false); }
+    else        { if (as_f16) ZTVM_DQ(4, false, true); else ZTVM_DQ(4, false, false); }
+  } else {
+    if (as_f16) ZTVM_DQ(3, true, true); else ZTVM_DQ(3, true, false);
+  }
+#undef ZTVM_DQ
+  return cudaGetLastError();
+}
+
+// ---- router top-k ------------------------------------------------------------------------------
+// One warp per token. Each lane keeps experts lane, lane+32, ... (up to 32 per lane, E <= 1024) in
+// registers. softmax over the E routed experts in f32, then K rounds of arg-max; ties go to the lower
+// expert index; the winner is masked with -1. Scores are written in descending order, then the shared
+// expert (index E) with sigmoid of its own logit when present (moe_router_topk.wgsl:83-135).
+constexpr int kTopkPerLane = 32;
+
+template <int PER>
+__global__ void __launch_bounds__(128) route_topk_kernel(const float* __restrict__ logits, uint32_t* __restrict__ ids,
+                                                          float* __restrict__ scores, uint32_t tokens, uint32_t E,
+                                                          uint32_t K, uint32_t norm_topk, uint32_t has_shared) {
+  const int lane = threadIdx.x & 31;
+  const uint32_t tok = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (tok >= tokens) return;
+  const float* l = logits + (size_t)tok * (E + has_shared);
+  const size_t obase = (size_t)tok * (K + has_shared);
+
+  float pv[PER];
+  float m = -3.0e38f;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const uint32_t e = (uint32_t)i * 32 + lane;
+    const float v = e < E ? l[e] : -3.0e38f;
+    pv[i] = v;
+    m = fmaxf(m, v);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const uint32_t e = (uint32_t)i * 32 + lane;
+    const float v = e < E ? expf(pv[i] - m) : 0.f;
+    pv[i] = e < E ? v : -1.f;
+    s += e < E ? v : 0.f;
+  }
+  const float denom = warp_sum(s);
+
+  float total = 0.f;
+  float my_top = 0.f;  // lane k keeps the k-th winner
+  for (uint32_t k = 0; k < K; ++k) {
+    float bv = -1.f;
+    uint32_t bi = 0xffffffffu;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {  // ascending expert index within the lane: strict > keeps the lower one
+      if (pv[i] > bv) { bv = pv[i]; bi = (uint32_t)i * 32 + lane; }
+    }
+    float best = bv;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) best = fmaxf(best, __shfl_xor_sync(0xffffffffu, best, o));
+    uint32_t widx = bv == best ? bi : 0xffffffffu;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) widx = min(widx, __shfl_xor_sync(0xffffffffu, widx, o));
+    total += best;
+    if ((uint32_t)lane == k) my_top = best;
+#pragma unroll
+    for (int i = 0; i < PER; ++i)
+      if ((uint32_t)i * 32 + lane == widx) pv[i] = -1.f;
+    if (lane == 0) ids[obase + k] = widx;
+  }
+  const float scale = norm_topk ? 1.0f / total : 1.0f / denom;
+  if ((uint32_t)lane < K) scores[obase + lane] = my_top * scale;
+  if (has_shared && lane == 0) {
+    ids[obase + K] = E;
+    scores[obase + K] = 1.0f / (1.0f + expf(-l[E]));
+  }
+}
+
+cudaError_t launch_route_topk(const float* logits, uint32_t* ids, float* scores, uint32_t tokens, uint32_t E,
+                              uint32_t K, bool norm_topk, bool has_shared, cudaStream_t st) {
+  const unsigned grid = (tokens + 3) / 4;
+  if (E <= 256) route_topk_kernel<8><<<grid, 128, 0, st>>>(logits, ids, scores, tokens, E, K, norm_topk, has_shared);
+  else route_topk_kernel<kTopkPerLane><<<grid, 128, 0, st>>>(logits, ids, scores, tokens, E, K, norm_topk, has_shared);
+  return cudaGetLastError();
+}
+
+// ---- SiLU * up -----------------------------------------------------------------------------------
+// Rows of [gate(ffn) | up(ffn)] f16 -> f16 [ffn]; f32 arithmetic (silu_mul.wgsl:40-43).
+__global__ void silu_mul_kernel(const __half* __restrict__ gate_up, __half* __restrict__ h, uint32_t rows, uint32_t ffn) {
+  const size_t total = (size_t)rows * ffn;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / ffn, c = i - r * ffn;
+    const float g = __half2float(gate_up[r * 2 * ffn + c]);
+    const float u = __half2float(gate_up[r * 2 * ffn + ffn + c]);
+    const float sg = g * (1.0f / (1.0f + expf(-g)));
+    h[i] = __float2half_rn(u * sg);
+  }
+}
+cudaError_t launch_silu_mul(const __half* gate_up, __half* h, uint32_t rows, uint32_t ffn, cudaStream_t st) {
+  const size_t total = (size_t)rows * ffn;
+  if (total == 0) return cudaSuccess;
+  silu_mul_kernel<<<grid_for(total, 256), 256, 0, st>>>(gate_up, h, rows, ffn);
+  return cudaGetLastError();
+}
+
+// ---- weighted combine -----------------------------------------------------------------------------
+// out[t][i] = f16(sum_s score[t][s] * f32(y[t][s][i])), slots added in index order (moe_combine.wgsl:39-43).
+__global__ void moe_combine_kernel(const __half* __restrict__ y, const float* __restrict__ scores, __half* __restrict__ out,
+                                   uint32_t tokens, uint32_t slots, uint32_t d) {
+  const size_t total = (size_t)tokens * d;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / d, c = i - t * d;
+    float acc = 0.f;
+    for (uint32_t s = 0; s < slots; ++s)
+      acc = __fadd_rn(acc, __fmul_rn(scores[t * slots + s], __half2float(y[(t * slots + s) * d + c])));
+    out[i] = __float2half_rn(acc);
+  }
+}
+cudaError_t launch_moe_combine(const __half* y_slots, const float* scores, __half* out, uint32_t tokens,
+                               uint32_t slots, uint32_t d, cudaStream_t st) {
+  const size_t total = (size_t)tokens * d;
+  if (total == 0) return cudaSuccess;
+  moe_combine_kernel<<<grid_for(total, 256), 256, 0, st>>>(y_slots, scores, out, tokens, slots, d);
+  return cudaGetLastError();
+}
+
+}  // namespace ztvm

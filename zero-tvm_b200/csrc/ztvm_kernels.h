@@ -1,0 +1,41 @@
+// Internal launch interfaces between the C-ABI layer (ztvm_api.cu) and the kernel files.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace ztvm {
+
+struct GemvParams {
+  const uint32_t* W;   // packed codes [N][KP] (MoE: [experts][N][KP])
+  const __half* S;     // scales [N][SPR]
+  const __half* B;     // biases [N][SPR], nullptr for the symmetric flavour
+  const __half* X;     // activations
+  void* Y;             // f16 or f32 output
+  uint32_t K, N, M;
+  uint32_t KP;           // words per weight row = K*bits/32
+  uint32_t SPR;          // scale groups per row = K/group
+  uint32_t group_shift;  // log2(group)
+  uint32_t out_f32;
+  uint32_t x_row_stride, y_row_stride;  // elements between batch rows
+  uint32_t tile_units;                  // set by the launcher
+  // MoE indirection (int4_matmul.gen.ts:216-225)
+  const uint32_t* ids;
+  uint32_t experts, in_slot_stride, out_slot_stride, in_tok_stride, out_tok_stride, ids_stride;
+  uint32_t* err_counter;
+};
+
+cudaError_t launch_gemv(GemvParams p, int bits, bool moe, uint32_t tokens, uint32_t slots, int sm_count,
+                        cudaStream_t st);
+
+cudaError_t launch_unpack_codes(const uint32_t* W, uint8_t* codes, uint32_t N, uint32_t K, int bits, cudaStream_t st);
+cudaError_t launch_dequant(const uint32_t* W, const __half* S, const __half* B, void* out, uint32_t N, uint32_t K,
+                           int bits, uint32_t group_shift, bool affine, bool as_f16, cudaStream_t st);
+
+cudaError_t launch_route_topk(const float* logits, uint32_t* ids, float* scores, uint32_t tokens, uint32_t E,
+                              uint32_t K, bool norm_topk, bool has_shared, cudaStream_t st);
+cudaError_t launch_silu_mul(const __half* gate_up, __half* h, uint32_t rows, uint32_t ffn, cudaStream_t st);
+cudaError_t launch_moe_combine(const __half* y_slots, const float* scores, __half* out, uint32_t tokens,
+                               uint32_t slots, uint32_t d, cudaStream_t st);
+
+}  // namespace ztvm
