@@ -215,6 +215,21 @@ def rel_err(y, y_ref, floor: float = 0.0) -> float:
     return float(r.max()) if r.size else 0.0
 
 
+def rel_err_scaled(y, y_ref, frac: float = 1e-3) -> float:
+    """rel_err with the floor tied to the output scale: floor = frac * rms(y_ref).
+
+    An f32 accumulation carries an absolute error proportional to the size of the
+    partial sums, so outputs that cancel to almost nothing cannot be held to a pure
+    relative bound by any f32 kernel (the reference's own f32 word order misses 2e-3
+    pure-relative on the 8192x2048 decode case). The reference grades with an absolute
+    floor of 1e-3 on O(1) outputs; this is the same floor made scale-free, so it also
+    fits the MoE down projection whose outputs are O(30).
+    """
+    y_ref = np.asarray(y_ref).astype(F64)
+    rms = float(np.sqrt(np.mean(y_ref * y_ref))) if y_ref.size else 0.0
+    return rel_err(y, y_ref, max(frac * rms, 1e-30))
+
+
 # --------------------------------------------------------------------------
 # MoE glue
 # --------------------------------------------------------------------------

@@ -8,7 +8,7 @@ from oracle import ztvm_oracle as zo
 from zero_tvm_b200.backend import moe_down_pod_args, moe_gate_pod_args, resolve_matmul
 
 pytestmark = pytest.mark.gpu
-TOL, FLOOR = 2e-3, 1e-3
+TOL = 2e-3   # with the scale-tied floor of oracle.rel_err_scaled (1e-3 of the output rms)
 
 
 def run_block(backend, dev, mb, K_top=8, bits=4):
@@ -50,12 +50,12 @@ def check_block(got, mb, oracle_c, K_top=8, bits=4):
     # each stage against the f64 anchor computed from the GPU's own (already checked) inputs
     g64 = oracle_c.moe_matmul_f64(mb["x"], *mb["gate"], ids_ref, ffn, d, 64, bits, in_per_slot=False)
     u64 = oracle_c.moe_matmul_f64(mb["x"], *mb["up"], ids_ref, ffn, d, 64, bits, in_per_slot=False)
-    assert zo.rel_err(got["gate_up"][..., :ffn], g64, FLOOR) <= TOL
-    assert zo.rel_err(got["gate_up"][..., ffn:], u64, FLOOR) <= TOL
+    assert zo.rel_err_scaled(got["gate_up"][..., :ffn], g64) <= TOL
+    assert zo.rel_err_scaled(got["gate_up"][..., ffn:], u64) <= TOL
     h_ref = oracle_c.silu_mul(got["gate_up"], ffn)
-    assert zo.rel_err(got["h"], h_ref.astype(np.float64), FLOOR) <= TOL
+    assert zo.rel_err_scaled(got["h"], h_ref.astype(np.float64)) <= TOL
     d64 = oracle_c.moe_matmul_f64(got["h"], *mb["down"], ids_ref, d, ffn, 64, bits, in_per_slot=True)
-    assert zo.rel_err(got["y_slots"], d64, FLOOR) <= TOL
+    assert zo.rel_err_scaled(got["y_slots"], d64) <= TOL
     y_ref = oracle_c.moe_combine(got["y_slots"], got["scores"])
     assert np.array_equal(got["y"].view(np.uint16), y_ref.view(np.uint16))
     assert np.isfinite(got["y"].astype(np.float32)).all()
@@ -90,7 +90,9 @@ def test_small_block(T, backend, dev, oracle_c):
     check_block(got, mb, oracle_c, K_top=4)
     # and against the whole-block numpy restatement (f16 intermediates where the engine stores f16)
     r = zo.moe_block(mb["x"], mb["logits"], mb["gate"], mb["up"], mb["down"], 16, 4, 128)
-    assert zo.rel_err(got["y"], r["y"].astype(np.float64), 1e-2) <= 5e-3   # real-weights.mjs block bound
+    # whole-block bound of the reference's real-weight test: 0.005 of max|ref| (tests/kernels/real-weights.mjs:72-73)
+    ref = r["y"].astype(np.float64)
+    assert np.abs(got["y"].astype(np.float64) - ref).max() <= 5e-3 * np.abs(ref).max()
 
 
 @pytest.mark.parametrize("T", [1, 16, 256])

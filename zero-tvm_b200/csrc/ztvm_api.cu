@@ -2,6 +2,7 @@
 // validates before it launches and reports through a status code plus a thread-local message.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 
@@ -10,6 +11,7 @@
 
 struct ztvm_ctx {
   uint32_t magic;
+  int gemv_path;  // 0 auto: M = 1 on the CUDA-core FMA GEMV, M = 2..8 on the matrix-unit GEMV; 1: FMA always; 2: matrix unit always (env ZTVM_GEMV_PATH=fma|mma, a measurement knob)
   int device;
   int sm_count;
   cudaStream_t stream;
@@ -75,6 +77,11 @@ ztvm_status check_desc(const ztvm_mm_desc* d, bool need_m) {
   return ZTVM_OK;
 }
 
+bool use_mma(const ztvm_ctx* ctx, const ztvm_mm_desc* d, uint32_t m) {
+  if (!ztvm::gemv_mma_supported((int)d->bits, d->group)) return false;
+  return ctx->gemv_path == 2 || (ctx->gemv_path == 0 && m > 1);
+}
+
 ztvm::GemvParams gemv_params(const ztvm_mm_desc* d, void* y, const void* x, const void* s, const void* w,
                              const void* b) {
   ztvm::GemvParams p;
@@ -99,8 +106,8 @@ ztvm_status check_buffers(const ztvm_mm_desc* d, const void* y, const void* x, c
   if (!y || !x || !s || !w) return fail(ZTVM_ERR_NULL_POINTER, "y/x/scales/packed_w must be non-NULL");
   if (d->affine && !b) return fail(ZTVM_ERR_NULL_POINTER, "affine weights need biases");
   if (!aligned(w, 16) || !aligned(x, 16)) return fail(ZTVM_ERR_ALIGNMENT, "packed_w and x must be 16-byte aligned");
-  if (!aligned(s, 2) || (b && !aligned(b, 2)) || !aligned(y, d->out_f32 ? 4 : 2))
-    return fail(ZTVM_ERR_ALIGNMENT, "scales/biases/y are misaligned for their element type");
+  if (!aligned(s, 8) || (b && !aligned(b, 8)) || !aligned(y, d->out_f32 ? 4 : 2))
+    return fail(ZTVM_ERR_ALIGNMENT, "scales/biases must be 8-byte aligned, y aligned to its element type");
   return ZTVM_OK;
 }
 
@@ -165,6 +172,8 @@ ztvm_status ztvm_init(int32_t device_ordinal, ztvm_ctx** out_ctx) {
     delete c;
     return cuda_fail(e, "context set-up");
   }
+  const char* gp = getenv("ZTVM_GEMV_PATH");
+  c->gemv_path = !gp ? 0 : !strcmp(gp, "fma") ? 1 : !strcmp(gp, "mma") ? 2 : 0;
   c->magic = kMagic;
   *out_ctx = c;
   return ZTVM_OK;
@@ -206,7 +215,8 @@ ztvm_status ztvm_int4_matmul(ztvm_ctx* ctx, const ztvm_mm_desc* d, void* y, cons
     p.X = static_cast<const __half*>(x) + (size_t)m0 * d->K;
     p.Y = d->out_f32 ? static_cast<void*>(static_cast<float*>(y) + (size_t)m0 * d->N)
                      : static_cast<void*>(static_cast<__half*>(y) + (size_t)m0 * d->N);
-    ZTVM_CUDA(ztvm::launch_gemv(p, (int)d->bits, false, 1, 1, ctx->sm_count, st));
+    if (use_mma(ctx, d, dd.M)) ZTVM_CUDA(ztvm::launch_gemv_mma(p, false, 1, 1, st));
+    else ZTVM_CUDA(ztvm::launch_gemv(p, (int)d->bits, false, 1, 1, ctx->sm_count, st));
   }
   return ZTVM_OK;
 }
@@ -264,7 +274,8 @@ ztvm_status ztvm_int4_matmul_moe(ztvm_ctx* ctx, const ztvm_moe_desc* md, void* y
     p.in_tok_stride = md->in_tok_stride; p.out_tok_stride = md->out_tok_stride;
     p.ids_stride = md->ids_stride;
     p.err_counter = ctx->err_counter;
-    ZTVM_CUDA(ztvm::launch_gemv(p, (int)d->bits, true, nt, md->slots, ctx->sm_count, st));
+    if (use_mma(ctx, d, 1)) ZTVM_CUDA(ztvm::launch_gemv_mma(p, true, nt, md->slots, st));
+    else ZTVM_CUDA(ztvm::launch_gemv(p, (int)d->bits, true, nt, md->slots, ctx->sm_count, st));
   }
   return ZTVM_OK;
 }

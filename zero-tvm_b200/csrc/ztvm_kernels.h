@@ -28,6 +28,10 @@ struct GemvParams {
 cudaError_t launch_gemv(GemvParams p, int bits, bool moe, uint32_t tokens, uint32_t slots, int sm_count,
                         cudaStream_t st);
 
+// 4-bit weights on the warp-level matrix unit (ztvm_gemv_mma.cu); M <= 8.
+bool gemv_mma_supported(int bits, uint32_t group);
+cudaError_t launch_gemv_mma(GemvParams p, bool moe, uint32_t tokens, uint32_t slots, cudaStream_t st);
+
 cudaError_t launch_unpack_codes(const uint32_t* W, uint8_t* codes, uint32_t N, uint32_t K, int bits, cudaStream_t st);
 cudaError_t launch_dequant(const uint32_t* W, const __half* S, const __half* B, void* out, uint32_t N, uint32_t K,
                            int bits, uint32_t group_shift, bool affine, bool as_f16, cudaStream_t st);
