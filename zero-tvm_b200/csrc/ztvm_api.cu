@@ -11,6 +11,7 @@
 
 struct ztvm_ctx {
   uint32_t magic;
+  int no_gemm;    // env ZTVM_NO_GEMM=1: keep M > 8 on GEMV slabs (a measurement knob)
   int gemv_path;  // 0 auto: M = 1 on the CUDA-core FMA GEMV, M = 2..8 on the matrix-unit GEMV; 1: FMA always; 2: matrix unit always (env ZTVM_GEMV_PATH=fma|mma, a measurement knob)
   int device;
   int sm_count;
@@ -172,6 +173,8 @@ ztvm_status ztvm_init(int32_t device_ordinal, ztvm_ctx** out_ctx) {
     delete c;
     return cuda_fail(e, "context set-up");
   }
+  const char* ng = getenv("ZTVM_NO_GEMM");
+  c->no_gemm = (ng && ng[0] == '1') ? 1 : 0;
   const char* gp = getenv("ZTVM_GEMV_PATH");
   c->gemv_path = !gp ? 0 : !strcmp(gp, "fma") ? 1 : !strcmp(gp, "mma") ? 2 : 0;
   c->magic = kMagic;
@@ -207,7 +210,15 @@ ztvm_status ztvm_int4_matmul(ztvm_ctx* ctx, const ztvm_mm_desc* d, void* y, cons
   if ((s = check_desc(d, true))) return s;
   if ((s = check_buffers(d, y, x, scales, packed_w, biases))) return s;
   cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : ctx->stream;
-  // Rows are processed in slabs of at most 8 by the GEMV.
+  if (d->M > 8 && ztvm::gemm_w4_supported((int)d->bits, d->group, d->K) && !ctx->no_gemm) {
+    if (!aligned(y, 16)) return fail(ZTVM_ERR_ALIGNMENT, "y must be 16-byte aligned for the GEMM path");
+    ZTVM_CUDA(ztvm::launch_gemm_w4(static_cast<const uint32_t*>(packed_w), static_cast<const __half*>(scales),
+                                   d->affine ? static_cast<const __half*>(biases) : nullptr,
+                                   static_cast<const __half*>(x), y, d->M, d->N, d->K, (uint32_t)log2_exact(d->group),
+                                   d->out_f32 != 0, ctx->err_counter + 1, st));
+    return ZTVM_OK;
+  }
+  // Otherwise rows are processed in slabs of at most 8 by the GEMV.
   for (uint32_t m0 = 0; m0 < d->M; m0 += 8) {
     ztvm_mm_desc dd = *d;
     dd.M = d->M - m0 < 8 ? d->M - m0 : 8;
@@ -348,8 +359,13 @@ ztvm_status ztvm_device_errors(ztvm_ctx* ctx, void* stream, uint32_t* count) {
   if (!count) return fail(ZTVM_ERR_NULL_POINTER, "count is NULL");
   if (stream) ZTVM_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
   ZTVM_CUDA(cudaStreamSynchronize(ctx->stream));
-  ZTVM_CUDA(cudaMemcpy(count, ctx->err_counter, 4, cudaMemcpyDeviceToHost));
-  ZTVM_CUDA(cudaMemset(ctx->err_counter, 0, 4));
+  uint32_t words[2] = {0, 0};
+  ZTVM_CUDA(cudaMemcpy(words, ctx->err_counter, 8, cudaMemcpyDeviceToHost));
+  ZTVM_CUDA(cudaMemset(ctx->err_counter, 0, 8));
+  *count = words[0];
+  if (words[1])
+    return fail(ZTVM_ERR_CUDA, "a bounded wait inside the tensor-core GEMM ran out (stage code %u); its output is invalid",
+                words[1]);
   return ZTVM_OK;
 }
 

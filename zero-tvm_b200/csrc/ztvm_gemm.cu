@@ -1,0 +1,471 @@
+// Prefill GEMM (M > 8) for 4-bit group-quantised weights on the 5th-generation tensor cores.
+//
+//   y[m, n] = sum_k x[m, k] * W16[n, k],   W16 = f16_rne(fl32(s * q + b))   (or s * (q - 7))
+//
+// W16 is the value the reference's numpy dequantiser produces (scripts/make-dsv2-layer-ref.py:108-116)
+// and what its matrix-unit GEMMs feed their f16 fragments (int4_matmul.gen.ts:1173-1178); accumulation is
+// f32 in tensor memory. kind::f16 takes the f16 activations unchanged, so x is never rounded.
+//
+// One CTA computes a (MB x 128 tokens) x (BN weight rows) tile:
+//   warp 0      TMA producer: activation tiles x[128 x 64] (128-byte swizzle) into a ring of STAGES slots
+//   warp 1      MMA issuer: one elected thread issues tcgen05.mma (M=128, N=BN, K=16) per 16-wide k step and
+//               per 128-token block, accumulators live in TMEM; tcgen05.commit releases the ring slot
+//   warps 2..9  dequantisers: two threads per weight row of the tile; per 64-wide k block a thread loads 16 bytes
+//               of codes and the group's scale/bias, builds 32 f16 weights with the SAME device function the
+//               parity hook uses, and writes them in the tensor core's K-major 128B-swizzled layout.
+//               After the main loop the same eight warps drain TMEM (tcgen05.ld) and store y.
+// Every mbarrier wait is bounded (about a second); a wait that runs out raises a status word, the roles
+// stop, in-flight copies are waited for (bounded), TMEM is freed and the kernel returns.
+#include <cuda.h>
+
+#include "ztvm_device.cuh"
+#include "ztvm_kernels.h"
+
+namespace ztvm {
+
+constexpr int kGemmBK = 64;         // k elements per stage = one 128-byte swizzle row of f16
+constexpr int kGemmStages = 4;
+constexpr int kGemmDqWarps = 8;      // dequantiser warps (two per SM sub-partition)
+constexpr int kGemmThreads = 64 + kGemmDqWarps * 32;   // TMA warp + MMA warp + dequantisers
+constexpr unsigned long long kWaitCycles = 2000000000ull;  // ~1 s at 2 GHz
+
+// ---- PTX wrappers ------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false (and a raised status word) when the phase does not complete in about a second.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t* status, uint32_t code,
+                                          volatile uint32_t* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if ((unsigned long long)(clock64() - t0) > kWaitCycles) {
+      *abort_flag = 1u;
+      atomicExch(status, code);
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tmap, uint32_t bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// D[tmem] (+)= A[smem desc] * B[smem desc], f16 inputs, f32 accumulate
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor for a K-major tile whose rows are 128 bytes (64 f16) in the 128-byte
+// swizzle: 8-row groups are 1024 bytes apart (stride byte offset), the leading byte offset is unused,
+// descriptor version 1, layout type 2.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);          // start address >> 4, bits [0,14)
+  d |= (uint64_t)1 << 16;                            // leading byte offset (ignored for swizzled K-major)
+  d |= (uint64_t)(1024u >> 4) << 32;                 // stride byte offset, bits [32,46)
+  d |= (uint64_t)1 << 46;                            // descriptor version (Blackwell)
+  d |= (uint64_t)2 << 61;                            // SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor: f32 accumulate, f16 A and B, both K-major, M = 128, N = BN.
+__host__ __device__ constexpr uint32_t idesc_f16(int n) {
+  return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+
+// Weight = f16(fl32(s*q + b)). The codes come out of unpack4 as exact f16 integers; fma.rn.f32.f16
+// multiplies the two f16 operands exactly and adds the f32 bias with one rounding: the same bits as
+// dequant_w32<true> (s*q is exact in f32 either way), then one round-to-nearest-even to f16.
+// Dequantise one 8-code word into 8 f16 weights in natural order (as one uint4).
+template <bool AFFINE>
+__device__ __forceinline__ uint4 dequant_word_w16(uint32_t w, unsigned short s16, float sf, float b) {
+  const Codes8 c = unpack4(w);  // exact integer codes as f16 pairs (q0,q4)(q1,q5)(q2,q6)(q3,q7)
+  float v[8];
+  auto two = [&](const __half2& q2, int i_lo, int i_hi) {
+    uint32_t bits = *reinterpret_cast<const uint32_t*>(&q2);
+    unsigned short q_lo, q_hi;
+    asm("mov.b32 {%0,%1}, %2;" : "=h"(q_lo), "=h"(q_hi) : "r"(bits));
+    if (AFFINE) {
+      asm("fma.rn.f32.f16 %0, %1, %2, %3;" : "=f"(v[i_lo]) : "h"(s16), "h"(q_lo), "f"(b));
+      asm("fma.rn.f32.f16 %0, %1, %2, %3;" : "=f"(v[i_hi]) : "h"(s16), "h"(q_hi), "f"(b));
+    } else {
+      // s * (q - 7): q - 7 is exact in f16, the product of two f16 values is exact in f32
+      const __half2 q7 = __hsub2(q2, __float2half2_rn(7.0f));
+      const float2 f = __half22float2(q7);
+      v[i_lo] = sf * f.x;
+      v[i_hi] = sf * f.y;
+    }
+  };
+  two(c.p04, 0, 4);
+  two(c.p15, 1, 5);
+  two(c.p26, 2, 6);
+  two(c.p37, 3, 7);
+  uint4 o;
+  __half2 h;
+  h = __floats2half2_rn(v[0], v[1]); o.x = *reinterpret_cast<uint32_t*>(&h);
+  h = __floats2half2_rn(v[2], v[3]); o.y = *reinterpret_cast<uint32_t*>(&h);
+  h = __floats2half2_rn(v[4], v[5]); o.z = *reinterpret_cast<uint32_t*>(&h);
+  h = __floats2half2_rn(v[6], v[7]); o.w = *reinterpret_cast<uint32_t*>(&h);
+  return o;
+}
+
+struct GemmParams {
+  const uint32_t* W;
+  const __half* S;
+  const __half* B;   // nullptr: symmetric
+  void* Y;
+  uint32_t M, N, K, KP, SPR, group_shift, out_f32;
+  uint32_t* status;  // [1]: timeout code
+};
+
+// Dynamic shared memory carve-up (1024-byte aligned): A ring | B ring | barriers | tmem slot | abort flag
+template <int MB, int BN>
+struct GemmSmem {
+  static constexpr int kABytes = MB * 128 * kGemmBK * 2;  // per stage
+  static constexpr int kBBytes = BN * kGemmBK * 2;
+  static constexpr int kOffB = kGemmStages * kABytes;
+  static constexpr int kOffBar = kOffB + kGemmStages * kBBytes;
+  static constexpr int kTotal = kOffBar + 256;
+};
+
+template <int MB, int BN, bool AFFINE>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  using L = GemmSmem<MB, BN>;
+  // align the dynamic region to 1024 bytes (swizzle atoms and UMMA descriptors assume it)
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t a_ring = base, b_ring = base + L::kOffB, bars = base + L::kOffBar;
+  // barrier layout: full_a[S], full_b[S], empty[S], accum, then tmem slot (u32) and abort flag (u32)
+  auto bar_full_a = [&](int s) { return bars + 8u * s; };
+  auto bar_full_b = [&](int s) { return bars + 8u * (kGemmStages + s); };
+  auto bar_empty = [&](int s) { return bars + 8u * (2 * kGemmStages + s); };
+  const uint32_t bar_accum = bars + 8u * (3 * kGemmStages);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + L::kOffBar + 8 * (3 * kGemmStages + 1));
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t n0 = blockIdx.x * BN;
+  const uint32_t m0 = blockIdx.y * (MB * 128);
+  const uint32_t num_kb = p.K / kGemmBK;
+  constexpr uint32_t kTmemCols = (MB * BN) <= 32 ? 32 : (MB * BN) <= 64 ? 64 : (MB * BN) <= 128 ? 128 : (MB * BN) <= 256 ? 256 : 512;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kGemmStages; ++s) {
+      mbar_init(bar_full_a(s), 1);
+      mbar_init(bar_full_b(s), kGemmDqWarps);   // one arrival per dequantiser warp
+      mbar_init(bar_empty(s), 1);
+    }
+    mbar_init(bar_accum, 1);
+    *abort_flag = 0u;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {  // the MMA warp owns the TMEM allocation
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ================= TMA producer =================
+    if (lane == 0) {
+      uint32_t issued = 0;
+      for (uint32_t kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % kGemmStages;
+        const uint32_t ph = (kb / kGemmStages) & 1u;
+        if (kb >= kGemmStages && !mbar_wait(bar_empty(s), ph ^ 1u, p.status, 1u, abort_flag)) break;
+        mbar_arrive_expect_tx(bar_full_a(s), (uint32_t)L::kABytes);
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb)
+          tma_load_2d(a_ring + s * L::kABytes + mb * (128 * kGemmBK * 2), &tmap_x, bar_full_a(s), (int)(kb * kGemmBK),
+                      (int)(m0 + mb * 128));
+        issued = kb + 1;
+      }
+      // if the consumer stopped, wait (bounded) until the copies already issued have landed
+      if (*abort_flag) {
+        const uint32_t first = issued > (uint32_t)kGemmStages ? issued - kGemmStages : 0u;
+        for (uint32_t kb = first; kb < issued; ++kb) {
+          const long long t0 = clock64();
+          while (!mbar_try_wait(bar_full_a(kb % kGemmStages), (kb / kGemmStages) & 1u) &&
+                 (unsigned long long)(clock64() - t0) < kWaitCycles) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ================= MMA issuer =================
+    if (lane == 0) {
+      constexpr uint32_t idesc = idesc_f16(BN);
+      bool ok = true;
+      for (uint32_t kb = 0; kb < num_kb && ok; ++kb) {
+        const int s = kb % kGemmStages;
+        const uint32_t ph = (kb / kGemmStages) & 1u;
+        ok = mbar_wait(bar_full_a(s), ph, p.status, 2u, abort_flag) && mbar_wait(bar_full_b(s), ph, p.status, 3u, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const uint64_t bdesc = smem_desc_sw128(b_ring + s * L::kBBytes);
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb) {
+          const uint64_t adesc = smem_desc_sw128(a_ring + s * L::kABytes + mb * (128 * kGemmBK * 2));
+#pragma unroll
+          for (int k = 0; k < kGemmBK / 16; ++k) {
+            // advance both descriptors by 16 elements = 32 bytes inside the swizzle row: +2 in the (>>4) address field
+            umma_f16(tmem_base + (uint32_t)(mb * BN), adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
+                     (kb | (uint32_t)k) ? 1u : 0u);
+          }
+        }
+        umma_commit(bar_empty(s));   // the slot is free once these MMAs have read it
+      }
+      if (ok) umma_commit(bar_accum);  // all accumulators final
+    }
+  } else {
+    // ================= dequantisers (warps 2..9), then epilogue =================
+    const int t = threadIdx.x - 64;                  // 0..255
+    constexpr int TPR = (kGemmDqWarps * 32) / BN;    // threads per weight row (BN = 128 -> 2, 64 -> 4, 256 -> 1)
+    constexpr int WPT = (kGemmBK / 8) / TPR;         // 8-code words per thread per k block (4, 2, 8)
+    static_assert(TPR >= 1 && WPT >= 2 && TPR * WPT == 8, "unsupported BN");
+    const int gshift = (int)p.group_shift;
+    const uint32_t r_tile = (uint32_t)(t / TPR);     // weight row within the tile
+    const uint32_t part = (uint32_t)(t % TPR);       // which run of WPT words of the 8-word k block
+    const uint32_t row = min(n0 + r_tile, p.N - 1);
+    const uint32_t* wrow = p.W + (size_t)row * p.KP + part * WPT;
+    const unsigned short* srow = reinterpret_cast<const unsigned short*>(p.S) + (size_t)row * p.SPR;
+    const unsigned short* brow = reinterpret_cast<const unsigned short*>(p.B) + (size_t)row * p.SPR;
+    bool ok = true;
+    // Register ring, one entry per pipeline stage: codes, scale and bias of the k block that will go into that
+    // stage next. Entries are refilled right after use, so a global load has kGemmStages-1 k blocks to land.
+    struct Pre {
+      uint32_t w[WPT];
+      unsigned short s16, b16;
+    };
+    Pre ring[kGemmStages];
+    auto prefetch = [&](Pre& e, uint32_t kb) {
+      if (kb >= num_kb) return;
+      const uint32_t* wp = wrow + (size_t)kb * (kGemmBK / 8);
+      if constexpr (WPT == 2) {
+        asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(e.w[0]), "=r"(e.w[1]) : "l"(wp));
+      } else {
+#pragma unroll
+        for (int j = 0; j < WPT / 4; ++j) {
+          const uint4 v = ld_stream_u4(wp + j * 4);
+          e.w[4 * j] = v.x; e.w[4 * j + 1] = v.y; e.w[4 * j + 2] = v.z; e.w[4 * j + 3] = v.w;
+        }
+      }
+      // a thread's words lie inside one scale group for every supported group size (32, 64, 128) when WPT <= 4;
+      // with WPT == 8 and group 32 the two halves differ, handled below by reloading per half
+      const uint32_t g = (kb * kGemmBK + part * WPT * 8) >> gshift;
+      e.s16 = __ldg(srow + g);
+      e.b16 = AFFINE ? __ldg(brow + g) : (unsigned short)0;
+    };
+#pragma unroll
+    for (int s = 0; s < kGemmStages; ++s) prefetch(ring[s], (uint32_t)s);
+
+    uint8_t* const brow_sm = gen_base + L::kOffB + (r_tile >> 3) * 1024 + (r_tile & 7) * 128;
+    for (uint32_t kb0 = 0; kb0 < num_kb && ok; kb0 += kGemmStages) {
+#pragma unroll
+      for (int s = 0; s < kGemmStages; ++s) {
+        const uint32_t kb = kb0 + s;
+        if (kb >= num_kb || !ok) break;
+        const uint32_t ph = (kb / kGemmStages) & 1u;
+        if (kb >= kGemmStages) ok = mbar_wait(bar_empty(s), ph ^ 1u, p.status, 4u, abort_flag);
+        if (ok) {
+          const Pre& e = ring[s];
+          uint8_t* rowp = brow_sm + s * L::kBBytes;
+          float sf = __half2float(__ushort_as_half(e.s16));
+          float bf = __half2float(__ushort_as_half(e.b16));
+          unsigned short s16 = e.s16;
+#pragma unroll
+          for (int wi = 0; wi < WPT; ++wi) {
+            if (WPT == 8 && wi == 4 && gshift == 5) {   // group 32: the second half of the block is the next group
+              const uint32_t g = (kb * kGemmBK + 32) >> gshift;
+              s16 = __ldg(srow + g);
+              sf = __half2float(__ushort_as_half(s16));
+              bf = AFFINE ? __half2float(__ushort_as_half(__ldg(brow + g))) : 0.f;
+            }
+            const uint4 v = dequant_word_w16<AFFINE>(e.w[wi], s16, sf, bf);
+            const uint32_t chunk = part * WPT + wi;                      // 16-byte chunk of the 128-byte row
+            *reinterpret_cast<uint4*>(rowp + ((chunk ^ (r_tile & 7)) << 4)) = v;
+          }
+          fence_proxy_async();   // make the generic-proxy stores visible to the tensor core's async proxy
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_full_b(s));   // arrive even on abort so nobody waits on this warp
+        prefetch(ring[s], kb + kGemmStages);
+      }
+    }
+    // ---- epilogue: TMEM -> registers -> y ---------------------------------------------------------
+    const bool acc_ok = ok && mbar_wait(bar_accum, 0u, p.status, 5u, abort_flag);
+    tc_fence_after();
+    if (acc_ok) {
+      const int quarter = warp & 3;                      // TMEM lanes this warp may read: [32*quarter, +32)
+      const int half = (warp - 2) >> 2;                  // two warps share a quarter: even / odd column blocks
+#pragma unroll 1
+      for (int mb = 0; mb < MB; ++mb) {
+        const uint32_t m = m0 + mb * 128 + quarter * 32 + lane;
+#pragma unroll 1
+        for (int cb = half; cb < BN / 32; cb += 2) {
+          uint32_t v[32];
+          tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mb * BN + cb * 32), v);
+          tmem_ld_wait();
+          const uint32_t n = n0 + cb * 32;
+          if (m < p.M && n < p.N) {
+            if (p.out_f32) {
+              float* dst = reinterpret_cast<float*>(p.Y) + (size_t)m * p.N + n;
+              if (n + 32 <= p.N && (p.N & 3u) == 0) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                  reinterpret_cast<float4*>(dst)[i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                                                                  __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+              } else {
+                for (int i = 0; i < 32 && n + i < p.N; ++i) dst[i] = __uint_as_float(v[i]);
+              }
+            } else {
+              __half* dst = reinterpret_cast<__half*>(p.Y) + (size_t)m * p.N + n;
+              if (n + 32 <= p.N && (p.N & 7u) == 0) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  uint4 o;
+                  __half2 h;
+                  h = __floats2half2_rn(__uint_as_float(v[8 * i]), __uint_as_float(v[8 * i + 1])); o.x = *reinterpret_cast<uint32_t*>(&h);
+                  h = __floats2half2_rn(__uint_as_float(v[8 * i + 2]), __uint_as_float(v[8 * i + 3])); o.y = *reinterpret_cast<uint32_t*>(&h);
+                  h = __floats2half2_rn(__uint_as_float(v[8 * i + 4]), __uint_as_float(v[8 * i + 5])); o.z = *reinterpret_cast<uint32_t*>(&h);
+                  h = __floats2half2_rn(__uint_as_float(v[8 * i + 6]), __uint_as_float(v[8 * i + 7])); o.w = *reinterpret_cast<uint32_t*>(&h);
+                  reinterpret_cast<uint4*>(dst)[i] = o;
+                }
+              } else {
+                for (int i = 0; i < 32 && n + i < p.N; ++i) dst[i] = __float2half_rn(__uint_as_float(v[i]));
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// ---- host side --------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+template <int MB, int BN, bool AFFINE>
+static cudaError_t launch_gemm_one(const CUtensorMap& tmap, const GemmParams& p, cudaStream_t st) {
+  auto kern = gemm_w4_kernel<MB, BN, AFFINE>;
+  constexpr int smem = GemmSmem<MB, BN>::kTotal + 1024;
+  static bool attr_set[16] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 16 && !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    attr_set[dev] = true;
+  }
+  dim3 grid((p.N + BN - 1) / BN, (p.M + MB * 128 - 1) / (MB * 128));
+  kern<<<grid, kGemmThreads, smem, st>>>(tmap, p);
+  return cudaGetLastError();
+}
+
+bool gemm_w4_supported(int bits, uint32_t group, uint32_t K) {
+  return bits == 4 && (group == 32 || group == 64 || group == 128) && K % kGemmBK == 0;
+}
+
+cudaError_t launch_gemm_w4(const uint32_t* W, const __half* S, const __half* B, const __half* X, void* Y, uint32_t M,
+                           uint32_t N, uint32_t K, uint32_t group_shift, bool out_f32, uint32_t* status, cudaStream_t st) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return cudaErrorNotSupported;
+  CUtensorMap tmap;
+  const cuuint64_t dims[2] = {K, M};
+  const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)kGemmBK, 128};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(X), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+  GemmParams p;
+  p.W = W; p.S = S; p.B = B; p.Y = Y;
+  p.M = M; p.N = N; p.K = K; p.KP = K / 8; p.SPR = K >> group_shift; p.group_shift = group_shift;
+  p.out_f32 = out_f32 ? 1u : 0u;
+  p.status = status;
+  const bool affine = B != nullptr;
+  if (M > 128) {
+    return affine ? launch_gemm_one<2, 128, true>(tmap, p, st) : launch_gemm_one<2, 128, false>(tmap, p, st);
+  }
+  return affine ? launch_gemm_one<1, 64, true>(tmap, p, st) : launch_gemm_one<1, 64, false>(tmap, p, st);
+}
+
+}  // namespace ztvm

@@ -32,6 +32,12 @@ cudaError_t launch_gemv(GemvParams p, int bits, bool moe, uint32_t tokens, uint3
 bool gemv_mma_supported(int bits, uint32_t group);
 cudaError_t launch_gemv_mma(GemvParams p, bool moe, uint32_t tokens, uint32_t slots, cudaStream_t st);
 
+// 4-bit weights, M > 8: tcgen05 GEMM with TMEM accumulators (ztvm_gemm.cu). status[0] receives a non-zero code
+// if a pipeline wait inside the kernel ran out.
+bool gemm_w4_supported(int bits, uint32_t group, uint32_t K);
+cudaError_t launch_gemm_w4(const uint32_t* W, const __half* S, const __half* B, const __half* X, void* Y, uint32_t M,
+                           uint32_t N, uint32_t K, uint32_t group_shift, bool out_f32, uint32_t* status, cudaStream_t st);
+
 cudaError_t launch_unpack_codes(const uint32_t* W, uint8_t* codes, uint32_t N, uint32_t K, int bits, cudaStream_t st);
 cudaError_t launch_dequant(const uint32_t* W, const __half* S, const __half* B, void* out, uint32_t N, uint32_t K,
                            int bits, uint32_t group_shift, bool affine, bool as_f16, cudaStream_t st);
