@@ -7,12 +7,14 @@
 // f32 in tensor memory. kind::f16 takes the f16 activations unchanged, so x is never rounded.
 //
 // One CTA computes a (MB x 128 tokens) x (BN weight rows) tile:
-//   warp 0      TMA producer: activation tiles x[128 x 64] (128-byte swizzle) into a ring of STAGES slots
+//   warp 0      TMA producer for activations: tiles x[128 x 64] (128-byte swizzle) into a ring of STAGES slots
 //   warp 1      MMA issuer: one elected thread issues tcgen05.mma (M=128, N=BN, K=16) per 16-wide k step and
 //               per 128-token block, accumulators live in TMEM; tcgen05.commit releases the ring slot
-//   warps 2..9  dequantisers: two threads per weight row of the tile; per 64-wide k block a thread loads 16 bytes
-//               of codes and the group's scale/bias, builds 32 f16 weights with the SAME device function the
-//               parity hook uses, and writes them in the tensor core's K-major 128B-swizzled layout.
+//   warp 2      TMA producer for packed weights: tiles W[BN rows x 32 words] (= 256 codes, four k blocks, whole
+//               128-byte lines per row) into a ring of its own, so the code stream runs far ahead of its use
+//   warps 3..10 dequantisers: two threads per weight row of the tile; per 64-wide k block a thread reads 16 bytes
+//               of codes from shared memory and the group's scale/bias, builds 32 f16 weights with the SAME device
+//               function the parity hook uses, and writes them in the tensor core's K-major 128B-swizzled layout.
 //               After the main loop the same eight warps drain TMEM (tcgen05.ld) and store y.
 // Every mbarrier wait is bounded (about a second); a wait that runs out raises a status word, the roles
 // stop, in-flight copies are waited for (bounded), TMEM is freed and the kernel returns.
@@ -24,9 +26,11 @@
 namespace ztvm {
 
 constexpr int kGemmBK = 64;         // k elements per stage = one 128-byte swizzle row of f16
-constexpr int kGemmStages = 4;
+constexpr int kGemmStages = 3;       // activation / dequantised-weight ring
+constexpr int kGemmWStages = 3;      // packed-weight ring (each slot holds four k blocks)
+constexpr int kGemmWChunk = 4;       // k blocks per packed-weight slot: 32 words = 128 bytes per row
 constexpr int kGemmDqWarps = 8;      // dequantiser warps (two per SM sub-partition)
-constexpr int kGemmThreads = 64 + kGemmDqWarps * 32;   // TMA warp + MMA warp + dequantisers
+constexpr int kGemmThreads = 96 + kGemmDqWarps * 32;   // two TMA warps + MMA warp + dequantisers
 constexpr unsigned long long kWaitCycles = 2000000000ull;  // ~1 s at 2 GHz
 
 // ---- PTX wrappers ------------------------------------------------------------------------------------
@@ -180,25 +184,30 @@ struct GemmSmem {
   static constexpr int kABytes = MB * 128 * kGemmBK * 2;  // per stage
   static constexpr int kBBytes = BN * kGemmBK * 2;
   static constexpr int kOffB = kGemmStages * kABytes;
-  static constexpr int kOffBar = kOffB + kGemmStages * kBBytes;
+  static constexpr int kWBytes = BN * 128;                 // per packed-weight slot
+  static constexpr int kOffW = kOffB + kGemmStages * kBBytes;
+  static constexpr int kOffBar = kOffW + kGemmWStages * kWBytes;
   static constexpr int kTotal = kOffBar + 256;
 };
 
 template <int MB, int BN, bool AFFINE>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
+gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   using L = GemmSmem<MB, BN>;
   // align the dynamic region to 1024 bytes (swizzle atoms and UMMA descriptors assume it)
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t a_ring = base, b_ring = base + L::kOffB, bars = base + L::kOffBar;
-  // barrier layout: full_a[S], full_b[S], empty[S], accum, then tmem slot (u32) and abort flag (u32)
+  const uint32_t a_ring = base, b_ring = base + L::kOffB, w_ring = base + L::kOffW, bars = base + L::kOffBar;
+  // barrier layout: full_a[S], full_b[S], empty[S], w_full[WS], w_empty[WS], accum, then tmem slot and abort flag
   auto bar_full_a = [&](int s) { return bars + 8u * s; };
   auto bar_full_b = [&](int s) { return bars + 8u * (kGemmStages + s); };
   auto bar_empty = [&](int s) { return bars + 8u * (2 * kGemmStages + s); };
-  const uint32_t bar_accum = bars + 8u * (3 * kGemmStages);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + L::kOffBar + 8 * (3 * kGemmStages + 1));
+  auto bar_w_full = [&](int s) { return bars + 8u * (3 * kGemmStages + s); };
+  auto bar_w_empty = [&](int s) { return bars + 8u * (3 * kGemmStages + kGemmWStages + s); };
+  constexpr int kNumBars = 3 * kGemmStages + 2 * kGemmWStages + 1;
+  const uint32_t bar_accum = bars + 8u * (kNumBars - 1);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + L::kOffBar + 8 * kNumBars);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -212,6 +221,10 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
       mbar_init(bar_full_a(s), 1);
       mbar_init(bar_full_b(s), kGemmDqWarps);   // one arrival per dequantiser warp
       mbar_init(bar_empty(s), 1);
+    }
+    for (int s = 0; s < kGemmWStages; ++s) {
+      mbar_init(bar_w_full(s), 1);
+      mbar_init(bar_w_empty(s), kGemmDqWarps);
     }
     mbar_init(bar_accum, 1);
     *abort_flag = 0u;
@@ -277,9 +290,31 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
       }
       if (ok) umma_commit(bar_accum);  // all accumulators final
     }
+  } else if (warp == 2) {
+    // ================= TMA producer: packed weights =================
+    if (lane == 0) {
+      const uint32_t num_chunks = (num_kb + kGemmWChunk - 1) / kGemmWChunk;
+      uint32_t issued = 0;
+      for (uint32_t c = 0; c < num_chunks; ++c) {
+        const int s = c % kGemmWStages;
+        const uint32_t ph = (c / kGemmWStages) & 1u;
+        if (c >= kGemmWStages && !mbar_wait(bar_w_empty(s), ph ^ 1u, p.status, 6u, abort_flag)) break;
+        mbar_arrive_expect_tx(bar_w_full(s), (uint32_t)L::kWBytes);
+        tma_load_2d(w_ring + s * L::kWBytes, &tmap_w, bar_w_full(s), (int)(c * 32), (int)n0);
+        issued = c + 1;
+      }
+      if (*abort_flag) {
+        const uint32_t first = issued > (uint32_t)kGemmWStages ? issued - kGemmWStages : 0u;
+        for (uint32_t c = first; c < issued; ++c) {
+          const long long t0 = clock64();
+          while (!mbar_try_wait(bar_w_full(c % kGemmWStages), (c / kGemmWStages) & 1u) &&
+                 (unsigned long long)(clock64() - t0) < kWaitCycles) {}
+        }
+      }
+    }
   } else {
-    // ================= dequantisers (warps 2..9), then epilogue =================
-    const int t = threadIdx.x - 64;                  // 0..255
+    // ================= dequantisers (warps 3..10), then epilogue =================
+    const int t = threadIdx.x - 96;                  // 0..255
     constexpr int TPR = (kGemmDqWarps * 32) / BN;    // threads per weight row (BN = 128 -> 2, 64 -> 4, 256 -> 1)
     constexpr int WPT = (kGemmBK / 8) / TPR;         // 8-code words per thread per k block (4, 2, 8)
     static_assert(TPR >= 1 && WPT >= 2 && TPR * WPT == 8, "unsupported BN");
@@ -287,52 +322,77 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
     const uint32_t r_tile = (uint32_t)(t / TPR);     // weight row within the tile
     const uint32_t part = (uint32_t)(t % TPR);       // which run of WPT words of the 8-word k block
     const uint32_t row = min(n0 + r_tile, p.N - 1);
-    const uint32_t* wrow = p.W + (size_t)row * p.KP + part * WPT;
     const unsigned short* srow = reinterpret_cast<const unsigned short*>(p.S) + (size_t)row * p.SPR;
     const unsigned short* brow = reinterpret_cast<const unsigned short*>(p.B) + (size_t)row * p.SPR;
     bool ok = true;
-    // Register ring, one entry per pipeline stage: codes, scale and bias of the k block that will go into that
-    // stage next. Entries are refilled right after use, so a global load has kGemmStages-1 k blocks to land.
-    struct Pre {
-      uint32_t w[WPT];
-      unsigned short s16, b16;
+    // Scales and biases: eight groups per 16-byte load (group 64 = one group per k block) when the row's group
+    // count keeps the loads aligned, fetched eight k blocks ahead; scalar loads otherwise.
+    const bool vec_sb = gshift == 6 && (p.SPR % 8u) == 0 && ((reinterpret_cast<uintptr_t>(p.S) | reinterpret_cast<uintptr_t>(p.B)) & 15u) == 0;
+    uint4 sv_cur = make_uint4(0, 0, 0, 0), bv_cur = sv_cur, sv_nxt = sv_cur, bv_nxt = sv_cur;
+    auto load_sb8 = [&](uint4& sv, uint4& bv, uint32_t kb8) {   // groups kb8 .. kb8+7
+      if (kb8 >= num_kb) return;
+      sv = __ldg(reinterpret_cast<const uint4*>(srow + kb8));
+      if (AFFINE) bv = __ldg(reinterpret_cast<const uint4*>(brow + kb8));
     };
-    Pre ring[kGemmStages];
-    auto prefetch = [&](Pre& e, uint32_t kb) {
-      if (kb >= num_kb) return;
-      const uint32_t* wp = wrow + (size_t)kb * (kGemmBK / 8);
-      if constexpr (WPT == 2) {
-        asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(e.w[0]), "=r"(e.w[1]) : "l"(wp));
-      } else {
-#pragma unroll
-        for (int j = 0; j < WPT / 4; ++j) {
-          const uint4 v = ld_stream_u4(wp + j * 4);
-          e.w[4 * j] = v.x; e.w[4 * j + 1] = v.y; e.w[4 * j + 2] = v.z; e.w[4 * j + 3] = v.w;
-        }
-      }
-      // a thread's words lie inside one scale group for every supported group size (32, 64, 128) when WPT <= 4;
-      // with WPT == 8 and group 32 the two halves differ, handled below by reloading per half
-      const uint32_t g = (kb * kGemmBK + part * WPT * 8) >> gshift;
-      e.s16 = __ldg(srow + g);
-      e.b16 = AFFINE ? __ldg(brow + g) : (unsigned short)0;
+    auto pick16 = [](const uint4& v, int i) -> unsigned short {   // i is a compile-time constant after unrolling
+      const uint32_t wsel = (i >> 1) == 0 ? v.x : (i >> 1) == 1 ? v.y : (i >> 1) == 2 ? v.z : v.w;
+      return (unsigned short)((i & 1) ? (wsel >> 16) : (wsel & 0xFFFFu));
     };
-#pragma unroll
-    for (int s = 0; s < kGemmStages; ++s) prefetch(ring[s], (uint32_t)s);
+    if (vec_sb) { load_sb8(sv_cur, bv_cur, 0); load_sb8(sv_nxt, bv_nxt, 8); }
 
-    uint8_t* const brow_sm = gen_base + L::kOffB + (r_tile >> 3) * 1024 + (r_tile & 7) * 128;
-    for (uint32_t kb0 = 0; kb0 < num_kb && ok; kb0 += kGemmStages) {
+    // this thread's row inside a swizzled tile (dequantised ring and packed ring share the row geometry)
+    const uint32_t row_off = (r_tile >> 3) * 1024 + (r_tile & 7) * 128;
+    uint8_t* const brow_sm = gen_base + L::kOffB + row_off;
+    const uint8_t* const wrow_sm = gen_base + L::kOffW + row_off;
+    constexpr int kUnroll = 8;   // = groups per scale vector; a multiple of kGemmWChunk
+    for (uint32_t kb0 = 0; kb0 < num_kb && ok; kb0 += kUnroll) {
 #pragma unroll
-      for (int s = 0; s < kGemmStages; ++s) {
-        const uint32_t kb = kb0 + s;
+      for (int i = 0; i < kUnroll; ++i) {
+        const uint32_t kb = kb0 + i;
         if (kb >= num_kb || !ok) break;
+        const int s = (int)(kb % kGemmStages);
         const uint32_t ph = (kb / kGemmStages) & 1u;
-        if (kb >= kGemmStages) ok = mbar_wait(bar_empty(s), ph ^ 1u, p.status, 4u, abort_flag);
+        const uint32_t c = kb / kGemmWChunk;              // packed-weight chunk and slot
+        const int ws = (int)(c % kGemmWStages);
+        constexpr int kJ = kGemmWChunk;
+        const int j = i % kJ;                             // k block inside the chunk (kb0 is a multiple of 8)
+        if (j == 0) ok = mbar_wait(bar_w_full(ws), (c / kGemmWStages) & 1u, p.status, 7u, abort_flag);
+        // codes of this k block: words [j*8 + part*WPT, +WPT) of the row's 32-word line
+        uint32_t wv[WPT];
         if (ok) {
-          const Pre& e = ring[s];
+          const uint8_t* wl = wrow_sm + ws * L::kWBytes;
+#pragma unroll
+          for (int q4 = 0; q4 < (WPT + 3) / 4; ++q4) {
+            const uint32_t word0 = (uint32_t)j * 8 + part * WPT + q4 * 4;
+            const uint32_t chunk16 = word0 >> 2;
+            const uint8_t* src = wl + ((chunk16 ^ (r_tile & 7)) << 4) + (word0 & 3) * 4;
+            if constexpr (WPT == 2) {
+              const uint2 v = *reinterpret_cast<const uint2*>(src);
+              wv[0] = v.x; wv[1] = v.y;
+            } else {
+              const uint4 v = *reinterpret_cast<const uint4*>(src);
+              wv[4 * q4] = v.x; wv[4 * q4 + 1] = v.y; wv[4 * q4 + 2] = v.z; wv[4 * q4 + 3] = v.w;
+            }
+          }
+        }
+        if (j == kJ - 1 || kb + 1 == num_kb) {   // last read of the slot: hand it back to the producer
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_w_empty(ws));
+        }
+        if (ok && kb >= (uint32_t)kGemmStages) ok = mbar_wait(bar_empty(s), ph ^ 1u, p.status, 4u, abort_flag);
+        if (ok) {
           uint8_t* rowp = brow_sm + s * L::kBBytes;
-          float sf = __half2float(__ushort_as_half(e.s16));
-          float bf = __half2float(__ushort_as_half(e.b16));
-          unsigned short s16 = e.s16;
+          unsigned short s16, b16 = 0;
+          if (vec_sb) {
+            s16 = pick16(sv_cur, i);
+            if (AFFINE) b16 = pick16(bv_cur, i);
+          } else {
+            const uint32_t g = (kb * kGemmBK + part * WPT * 8) >> gshift;
+            s16 = __ldg(srow + g);
+            if (AFFINE) b16 = __ldg(brow + g);
+          }
+          float sf = __half2float(__ushort_as_half(s16));
+          float bf = __half2float(__ushort_as_half(b16));
 #pragma unroll
           for (int wi = 0; wi < WPT; ++wi) {
             if (WPT == 8 && wi == 4 && gshift == 5) {   // group 32: the second half of the block is the next group
@@ -341,7 +401,7 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
               sf = __half2float(__ushort_as_half(s16));
               bf = AFFINE ? __half2float(__ushort_as_half(__ldg(brow + g))) : 0.f;
             }
-            const uint4 v = dequant_word_w16<AFFINE>(e.w[wi], s16, sf, bf);
+            const uint4 v = dequant_word_w16<AFFINE>(wv[wi], s16, sf, bf);
             const uint32_t chunk = part * WPT + wi;                      // 16-byte chunk of the 128-byte row
             *reinterpret_cast<uint4*>(rowp + ((chunk ^ (r_tile & 7)) << 4)) = v;
           }
@@ -349,7 +409,10 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_full_b(s));   // arrive even on abort so nobody waits on this warp
-        prefetch(ring[s], kb + kGemmStages);
+      }
+      if (vec_sb) {
+        sv_cur = sv_nxt; bv_cur = bv_nxt;
+        load_sb8(sv_nxt, bv_nxt, kb0 + 2 * kUnroll);
       }
     }
     // ---- epilogue: TMEM -> registers -> y ---------------------------------------------------------
@@ -357,7 +420,7 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
     tc_fence_after();
     if (acc_ok) {
       const int quarter = warp & 3;                      // TMEM lanes this warp may read: [32*quarter, +32)
-      const int half = (warp - 2) >> 2;                  // two warps share a quarter: even / odd column blocks
+      const int half = (warp - 3) >> 2;                  // two warps share a quarter: even / odd column blocks
 #pragma unroll 1
       for (int mb = 0; mb < MB; ++mb) {
         const uint32_t m = m0 + mb * 128 + quarter * 32 + lane;
@@ -423,7 +486,7 @@ static EncodeTiledFn get_encode_fn() {
 }
 
 template <int MB, int BN, bool AFFINE>
-static cudaError_t launch_gemm_one(const CUtensorMap& tmap, const GemmParams& p, cudaStream_t st) {
+static cudaError_t launch_gemm_one(const CUtensorMap& tmap, const CUtensorMap& tmap_w, const GemmParams& p, cudaStream_t st) {
   auto kern = gemm_w4_kernel<MB, BN, AFFINE>;
   constexpr int smem = GemmSmem<MB, BN>::kTotal + 1024;
   static bool attr_set[16] = {};
@@ -435,7 +498,7 @@ static cudaError_t launch_gemm_one(const CUtensorMap& tmap, const GemmParams& p,
     attr_set[dev] = true;
   }
   dim3 grid((p.N + BN - 1) / BN, (p.M + MB * 128 - 1) / (MB * 128));
-  kern<<<grid, kGemmThreads, smem, st>>>(tmap, p);
+  kern<<<grid, kGemmThreads, smem, st>>>(tmap, tmap_w, p);
   return cudaGetLastError();
 }
 
@@ -456,6 +519,16 @@ cudaError_t launch_gemm_w4(const uint32_t* W, const __half* S, const __half* B, 
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+  // packed weights: u32 [N][K/8], box = 32 words (four k blocks, one 128-byte line) x BN rows
+  const uint32_t bn = M > 128 ? 128u : 64u;
+  CUtensorMap tmap_w;
+  const cuuint64_t wdims[2] = {K / 8, N};
+  const cuuint64_t wstrides[1] = {(cuuint64_t)(K / 8) * 4};
+  const cuuint32_t wbox[2] = {32, bn};
+  r = enc(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint32_t*>(W), wdims, wstrides, wbox, estr,
+          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
   GemmParams p;
   p.W = W; p.S = S; p.B = B; p.Y = Y;
   p.M = M; p.N = N; p.K = K; p.KP = K / 8; p.SPR = K >> group_shift; p.group_shift = group_shift;
@@ -463,9 +536,9 @@ cudaError_t launch_gemm_w4(const uint32_t* W, const __half* S, const __half* B, 
   p.status = status;
   const bool affine = B != nullptr;
   if (M > 128) {
-    return affine ? launch_gemm_one<2, 128, true>(tmap, p, st) : launch_gemm_one<2, 128, false>(tmap, p, st);
+    return affine ? launch_gemm_one<2, 128, true>(tmap, tmap_w, p, st) : launch_gemm_one<2, 128, false>(tmap, tmap_w, p, st);
   }
-  return affine ? launch_gemm_one<1, 64, true>(tmap, p, st) : launch_gemm_one<1, 64, false>(tmap, p, st);
+  return affine ? launch_gemm_one<1, 64, true>(tmap, tmap_w, p, st) : launch_gemm_one<1, 64, false>(tmap, tmap_w, p, st);
 }
 
 }  // namespace ztvm
