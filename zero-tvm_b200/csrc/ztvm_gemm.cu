@@ -81,6 +81,15 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tma
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(c0), "r"(c1)
       : "memory");
 }
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, uint32_t src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(src), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit_and_wait() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
 }
@@ -176,6 +185,7 @@ struct GemmParams {
   void* Y;
   uint32_t M, N, K, KP, SPR, group_shift, out_f32;
   uint32_t* status;  // [1]: timeout code
+  uint32_t tma_store;  // 1: f16 output through shared memory + TMA store (needs N % 8 == 0)
 };
 
 // Dynamic shared memory carve-up (1024-byte aligned): A ring | B ring | barriers | tmem slot | abort flag
@@ -192,20 +202,21 @@ struct GemmSmem {
 
 template <int MB, int BN, bool AFFINE>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) {
+gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+               const __grid_constant__ CUtensorMap tmap_y, const GemmParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   using L = GemmSmem<MB, BN>;
   // align the dynamic region to 1024 bytes (swizzle atoms and UMMA descriptors assume it)
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t a_ring = base, b_ring = base + L::kOffB, w_ring = base + L::kOffW, bars = base + L::kOffBar;
-  // barrier layout: full_a[S], full_b[S], empty[S], w_full[WS], w_empty[WS], accum, then tmem slot and abort flag
-  auto bar_full_a = [&](int s) { return bars + 8u * s; };
-  auto bar_full_b = [&](int s) { return bars + 8u * (kGemmStages + s); };
-  auto bar_empty = [&](int s) { return bars + 8u * (2 * kGemmStages + s); };
-  auto bar_w_full = [&](int s) { return bars + 8u * (3 * kGemmStages + s); };
-  auto bar_w_empty = [&](int s) { return bars + 8u * (3 * kGemmStages + kGemmWStages + s); };
-  constexpr int kNumBars = 3 * kGemmStages + 2 * kGemmWStages + 1;
+  // barrier layout: full[S] (activation bytes + one arrival per dequantiser warp), empty[S], w_full[WS],
+  // w_empty[WS], accum, then tmem slot and abort flag
+  auto bar_full = [&](int s) { return bars + 8u * s; };
+  auto bar_empty = [&](int s) { return bars + 8u * (kGemmStages + s); };
+  auto bar_w_full = [&](int s) { return bars + 8u * (2 * kGemmStages + s); };
+  auto bar_w_empty = [&](int s) { return bars + 8u * (2 * kGemmStages + kGemmWStages + s); };
+  constexpr int kNumBars = 2 * kGemmStages + 2 * kGemmWStages + 1;
   const uint32_t bar_accum = bars + 8u * (kNumBars - 1);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + L::kOffBar + 8 * kNumBars);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(tmem_slot + 1);
@@ -218,8 +229,7 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kGemmStages; ++s) {
-      mbar_init(bar_full_a(s), 1);
-      mbar_init(bar_full_b(s), kGemmDqWarps);   // one arrival per dequantiser warp
+      mbar_init(bar_full(s), 1 + kGemmDqWarps);   // the TMA producer's arrival (with the byte count) + the dequantiser warps
       mbar_init(bar_empty(s), 1);
     }
     for (int s = 0; s < kGemmWStages; ++s) {
@@ -247,10 +257,10 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
         const int s = kb % kGemmStages;
         const uint32_t ph = (kb / kGemmStages) & 1u;
         if (kb >= kGemmStages && !mbar_wait(bar_empty(s), ph ^ 1u, p.status, 1u, abort_flag)) break;
-        mbar_arrive_expect_tx(bar_full_a(s), (uint32_t)L::kABytes);
+        mbar_arrive_expect_tx(bar_full(s), (uint32_t)L::kABytes);
 #pragma unroll
         for (int mb = 0; mb < MB; ++mb)
-          tma_load_2d(a_ring + s * L::kABytes + mb * (128 * kGemmBK * 2), &tmap_x, bar_full_a(s), (int)(kb * kGemmBK),
+          tma_load_2d(a_ring + s * L::kABytes + mb * (128 * kGemmBK * 2), &tmap_x, bar_full(s), (int)(kb * kGemmBK),
                       (int)(m0 + mb * 128));
         issued = kb + 1;
       }
@@ -259,7 +269,7 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
         const uint32_t first = issued > (uint32_t)kGemmStages ? issued - kGemmStages : 0u;
         for (uint32_t kb = first; kb < issued; ++kb) {
           const long long t0 = clock64();
-          while (!mbar_try_wait(bar_full_a(kb % kGemmStages), (kb / kGemmStages) & 1u) &&
+          while (!mbar_try_wait(bar_full(kb % kGemmStages), (kb / kGemmStages) & 1u) &&
                  (unsigned long long)(clock64() - t0) < kWaitCycles) {}
         }
       }
@@ -268,25 +278,31 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
     // ================= MMA issuer =================
     if (lane == 0) {
       constexpr uint32_t idesc = idesc_f16(BN);
-      bool ok = true;
-      for (uint32_t kb = 0; kb < num_kb && ok; ++kb) {
-        const int s = kb % kGemmStages;
-        const uint32_t ph = (kb / kGemmStages) & 1u;
-        ok = mbar_wait(bar_full_a(s), ph, p.status, 2u, abort_flag) && mbar_wait(bar_full_b(s), ph, p.status, 3u, abort_flag);
+      const uint64_t a0 = smem_desc_sw128(a_ring), b0 = smem_desc_sw128(b_ring);
+      uint32_t s = 0, ph = 0;
+      bool ok = true, ready = false;   // ready: the current stage's barrier was already seen complete by an early poll
+      for (uint32_t kb = 0; kb < num_kb; ++kb) {
+        if (!ready) ok = mbar_wait(bar_full(s), ph, p.status, 2u, abort_flag);
         if (!ok) break;
         tc_fence_after();
-        const uint64_t bdesc = smem_desc_sw128(b_ring + s * L::kBBytes);
+        const uint64_t bdesc = b0 + (uint64_t)(s * (L::kBBytes >> 4));
+        const uint32_t ns = s + 1 == (uint32_t)kGemmStages ? 0u : s + 1;
+        const uint32_t nph = ns == 0 ? ph ^ 1u : ph;
+        bool ready_next = false;
 #pragma unroll
         for (int mb = 0; mb < MB; ++mb) {
-          const uint64_t adesc = smem_desc_sw128(a_ring + s * L::kABytes + mb * (128 * kGemmBK * 2));
+          const uint64_t adesc = a0 + (uint64_t)(s * (L::kABytes >> 4) + mb * ((128 * kGemmBK * 2) >> 4));
 #pragma unroll
           for (int k = 0; k < kGemmBK / 16; ++k) {
             // advance both descriptors by 16 elements = 32 bytes inside the swizzle row: +2 in the (>>4) address field
             umma_f16(tmem_base + (uint32_t)(mb * BN), adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
                      (kb | (uint32_t)k) ? 1u : 0u);
+            // the tensor pipe is busy with what was just queued: poll the next stage's barrier in its shadow
+            if (mb == MB - 1 && k == kGemmBK / 16 - 2 && kb + 1 < num_kb) ready_next = mbar_try_wait(bar_full(ns), nph);
           }
         }
         umma_commit(bar_empty(s));   // the slot is free once these MMAs have read it
+        s = ns; ph = nph; ready = ready_next;
       }
       if (ok) umma_commit(bar_accum);  // all accumulators final
     }
@@ -408,7 +424,7 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
           fence_proxy_async();   // make the generic-proxy stores visible to the tensor core's async proxy
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_full_b(s));   // arrive even on abort so nobody waits on this warp
+        if (lane == 0) mbar_arrive(bar_full(s));   // arrive even on abort so nobody waits on this warp
       }
       if (vec_sb) {
         sv_cur = sv_nxt; bv_cur = bv_nxt;
@@ -418,7 +434,45 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
     // ---- epilogue: TMEM -> registers -> y ---------------------------------------------------------
     const bool acc_ok = ok && mbar_wait(bar_accum, 0u, p.status, 5u, abort_flag);
     tc_fence_after();
-    if (acc_ok) {
+    if (acc_ok && p.tma_store) {
+      // f16 output: registers -> shared memory in the 128-byte swizzle (two 64-column halves per 128-token block,
+      // in the activation ring, which is idle once the accumulators are final) -> one TMA store per half.
+      // The store clips rows past M and columns past N by itself.
+      const int quarter = warp & 3;                      // TMEM lanes this warp may read: [32*quarter, +32)
+      const int half = (warp - 3) >> 2;                  // two warps share a quarter: even / odd column blocks
+      const uint32_t r = (uint32_t)(quarter * 32 + lane);   // row (token) inside the 128-token block
+#pragma unroll 1
+      for (int mb = 0; mb < MB; ++mb) {
+#pragma unroll 1
+        for (int cb = half; cb < BN / 32; cb += 2) {
+          uint32_t v[32];
+          tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mb * BN + cb * 32), v);
+          tmem_ld_wait();
+          uint8_t* tile = gen_base + (mb * (BN / 64) + (cb >> 1)) * (128 * 128) + (r >> 3) * 1024 + (r & 7) * 128;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 o;
+            __half2 h;
+            h = __floats2half2_rn(__uint_as_float(v[8 * i]), __uint_as_float(v[8 * i + 1])); o.x = *reinterpret_cast<uint32_t*>(&h);
+            h = __floats2half2_rn(__uint_as_float(v[8 * i + 2]), __uint_as_float(v[8 * i + 3])); o.y = *reinterpret_cast<uint32_t*>(&h);
+            h = __floats2half2_rn(__uint_as_float(v[8 * i + 4]), __uint_as_float(v[8 * i + 5])); o.z = *reinterpret_cast<uint32_t*>(&h);
+            h = __floats2half2_rn(__uint_as_float(v[8 * i + 6]), __uint_as_float(v[8 * i + 7])); o.w = *reinterpret_cast<uint32_t*>(&h);
+            const uint32_t chunk = (uint32_t)((cb & 1) * 4 + i);
+            *reinterpret_cast<uint4*>(tile + ((chunk ^ (r & 7)) << 4)) = o;
+          }
+        }
+      }
+      fence_proxy_async();
+      asm volatile("bar.sync 1, %0;" ::"n"(kGemmDqWarps * 32) : "memory");   // the eight epilogue warps only
+      if (threadIdx.x == 96) {
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+          for (int hh = 0; hh < BN / 64; ++hh)
+            tma_store_2d(&tmap_y, base + (uint32_t)((mb * (BN / 64) + hh) * (128 * 128)), (int)(n0 + hh * 64), (int)(m0 + mb * 128));
+        tma_store_commit_and_wait();
+      }
+    } else if (acc_ok) {
       const int quarter = warp & 3;                      // TMEM lanes this warp may read: [32*quarter, +32)
       const int half = (warp - 3) >> 2;                  // two warps share a quarter: even / odd column blocks
 #pragma unroll 1
@@ -486,7 +540,7 @@ static EncodeTiledFn get_encode_fn() {
 }
 
 template <int MB, int BN, bool AFFINE>
-static cudaError_t launch_gemm_one(const CUtensorMap& tmap, const CUtensorMap& tmap_w, const GemmParams& p, cudaStream_t st) {
+static cudaError_t launch_gemm_one(const CUtensorMap& tmap, const CUtensorMap& tmap_w, const CUtensorMap& tmap_y, const GemmParams& p, cudaStream_t st) {
   auto kern = gemm_w4_kernel<MB, BN, AFFINE>;
   constexpr int smem = GemmSmem<MB, BN>::kTotal + 1024;
   static bool attr_set[16] = {};
@@ -498,7 +552,7 @@ static cudaError_t launch_gemm_one(const CUtensorMap& tmap, const CUtensorMap& t
     attr_set[dev] = true;
   }
   dim3 grid((p.N + BN - 1) / BN, (p.M + MB * 128 - 1) / (MB * 128));
-  kern<<<grid, kGemmThreads, smem, st>>>(tmap, tmap_w, p);
+  kern<<<grid, kGemmThreads, smem, st>>>(tmap, tmap_w, tmap_y, p);
   return cudaGetLastError();
 }
 
@@ -529,16 +583,28 @@ cudaError_t launch_gemm_w4(const uint32_t* W, const __half* S, const __half* B, 
           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+  // f16 output [M][N]: box = 64 columns (one 128-byte swizzle row) x 128 rows
+  CUtensorMap tmap_y = tmap_w;
+  const bool tma_store = !out_f32 && (N % 8 == 0) && ((reinterpret_cast<uintptr_t>(Y) & 15u) == 0);
+  if (tma_store) {
+    const cuuint64_t ydims[2] = {N, M};
+    const cuuint64_t ystrides[1] = {(cuuint64_t)N * 2};
+    const cuuint32_t ybox[2] = {64, 128};
+    r = enc(&tmap_y, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, Y, ydims, ystrides, ybox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+  }
   GemmParams p;
+  p.tma_store = tma_store ? 1u : 0u;
   p.W = W; p.S = S; p.B = B; p.Y = Y;
   p.M = M; p.N = N; p.K = K; p.KP = K / 8; p.SPR = K >> group_shift; p.group_shift = group_shift;
   p.out_f32 = out_f32 ? 1u : 0u;
   p.status = status;
   const bool affine = B != nullptr;
   if (M > 128) {
-    return affine ? launch_gemm_one<2, 128, true>(tmap, tmap_w, p, st) : launch_gemm_one<2, 128, false>(tmap, tmap_w, p, st);
+    return affine ? launch_gemm_one<2, 128, true>(tmap, tmap_w, tmap_y, p, st) : launch_gemm_one<2, 128, false>(tmap, tmap_w, tmap_y, p, st);
   }
-  return affine ? launch_gemm_one<1, 64, true>(tmap, tmap_w, p, st) : launch_gemm_one<1, 64, false>(tmap, tmap_w, p, st);
+  return affine ? launch_gemm_one<1, 64, true>(tmap, tmap_w, tmap_y, p, st) : launch_gemm_one<1, 64, false>(tmap, tmap_w, tmap_y, p, st);
 }
 
 }  // namespace ztvm
