@@ -12,8 +12,13 @@ Workloads
   decode_gemv        x[1,2048] times the same weight format, GB/s of algorithmic bytes.
   decode_layer_set   the 8B-class projections at M=1 (q,k,v,o,gate,up,down,lm_head), GB/s.
 
-With N > 1 every rank runs its own replica of the workload on its own weight sets (the single GEMM / GEMV
-does not shard); value is the aggregate over ranks divided by the slowest rank's device time.
+  layer_set_nshard   the same eight projections with their output rows sharded over the ranks and one all-gather
+                     per projection (strong scaling, GB/s of the whole layer set); --m-rows 1|4
+  moe_ep             35B-A3B-class MoE block (256 experts + shared, hidden 2048, ffn 512, top-8), experts sharded
+                     over the ranks, all-to-all dispatch / combine (strong scaling, TFLOP/s); --tokens T
+
+With N > 1 the first three workloads run as independent replicas, one per rank, on their own weight sets (a single
+GEMM / GEMV does not shard); value is the aggregate over ranks divided by the slowest rank's device time.
 """
 from __future__ import annotations
 
@@ -174,6 +179,113 @@ def run_reference_arm(args, rank):
     }))
 
 
+def run_sharded(args, rank, world, local):
+    """Row-sharded layer set / expert-parallel MoE: the two forms of the path that shard (zero-tvm_b200/sharded.py)."""
+    import torch
+    import torch.distributed as dist
+    import zero_tvm_b200 as z
+    from zero_tvm_b200 import sharded
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    be = z.backend.CudaMatmulBackend(local)
+    k = sharded.CudaKernels(be)
+    g = torch.Generator(device=device)
+    g.manual_seed(99)          # same weights on every rank, each keeps its shard
+
+    def rand_w(lead, N, K):
+        W = torch.randint(-2**31, 2**31 - 1, (*lead, N, K // 8), dtype=torch.int32, device=device, generator=g)
+        sc = (torch.randn((*lead, N, K // 64), device=device, generator=g) * 0.01).abs().to(torch.float16)
+        b = (torch.randn((*lead, N, K // 64), device=device, generator=g) * 0.05).to(torch.float16)
+        return W, sc, b
+
+    verified = None
+    if args.workload == "layer_set_nshard":
+        M = args.m_rows
+        projs, xs, total_bytes = [], [], 0
+        for name, N, K, f32 in z.synth.DENSE_LAYER_SET:
+            W, sc, b = rand_w((), N, K)
+            lo, hi = sharded.shard_rows(N, world, rank)
+            projs.append(sharded.NShardedProjection(k, W[lo:hi].contiguous(), sc[lo:hi].contiguous(), b[lo:hi].contiguous(),
+                                                    N, K, out_f32=f32))
+            xs.append(torch.randn((M, K), device=device, generator=g).to(torch.float16))
+            total_bytes += algorithmic_bytes(N, K, M, out_bytes=4 if f32 else 2)
+            if name == "k_proj" and rank == 0:
+                from oracle import ztvm_oracle_c as zc
+                y = projs[-1].forward(xs[-1], M)
+                y64 = zc.matmul_f64(xs[-1].cpu().numpy(), W.cpu().numpy().view(np.uint32), sc.cpu().numpy(), b.cpu().numpy(), 64)
+                fl = 1e-3 * float(np.sqrt(np.mean(y64 * y64)))
+                err = float(np.max(np.abs(y.float().cpu().numpy() - y64) / np.maximum(np.abs(y64), fl)))
+                verified = {"projection": name, "max_rel_err": err, "ok": bool(err <= 2e-3)}
+            elif name == "k_proj":
+                projs[-1].forward(xs[-1], M)
+
+        def step():
+            for pj, x in zip(projs, xs):
+                pj.forward(x, M)
+        units, unit, launches = total_bytes / 1e9, "GB/s", len(projs)
+        cfg = {"workload": args.workload, "M": M, "shapes": [n for n, *_ in z.synth.DENSE_LAYER_SET],
+               "parallelism": f"output rows / {world} + all-gather", "l2": "inputs larger than L2: 459 MB of weights per step"}
+        bound, peak = "hbm", measured_peaks()["hbm"] * world
+    else:
+        E, top_k, d, ffn, T = 256, 8, 2048, 512, args.tokens
+        epr = E // world
+        sel = torch.tensor(list(range(rank * epr, (rank + 1) * epr)) + [E], device=device)
+        stacks = []
+        for N, K in ((ffn, d), (ffn, d), (d, ffn)):
+            W, sc, b = rand_w((E + 1,), N, K)
+            stacks.append((W[sel].contiguous(), sc[sel].contiguous(), b[sel].contiguous()))
+            del W, sc, b
+        moe = sharded.ExpertParallelMoE(k, *stacks, E=E, top_k=top_k, d=d, ffn=ffn)
+        tl = max(1, T // world)
+        x = torch.randn((tl, d), device=device).to(torch.float16)
+        logits = torch.randn((tl, E + 1), device=device)
+
+        def step():
+            moe.forward(x, logits)
+        pairs = tl * world * (top_k + 1)
+        units, unit, launches = pairs * 3 * 2.0 * ffn * d / 1e12, "TFLOP/s", 9
+        cfg = {"workload": args.workload, "tokens": tl * world, "experts": E, "top_k": top_k, "hidden": d, "ffn": ffn,
+               "parallelism": f"experts / {world} + all-to-all", "l2": "inputs larger than L2: 455 MB of expert weights"}
+        bound, peak = "hbm", measured_peaks()["hbm"] * world
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        ev0.record()
+        for _ in range(args.steps):
+            step()
+        ev1.record()
+        torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1)
+    if world > 1:
+        t = torch.tensor([ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / args.steps
+    value = units / (ms_per_step * 1e-3)
+    out = {"metric": METRIC, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+           "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+           "dtype": "f16 x int4 -> f32 accumulate", "data": "synthetic", "config": cfg,
+           "gpu_launches": int(args.steps * launches), "clocks": clocks.summary(), "verified": verified}
+    if unit == "GB/s":
+        out["roofline"] = {"bound": bound, "achieved": value, "peak": peak, "unit": "GB/s", "frac": value / peak,
+                           "traffic": None, "peak_kind": "measured copy bandwidth x ranks"}
+    if rank == 0:
+        print(json.dumps(out))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -182,6 +294,8 @@ def main():
     ap.add_argument("--workload", default="prefill_gemm_m512")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--m-rows", type=int, default=1, help="activation rows of layer_set_nshard")
+    ap.add_argument("--tokens", type=int, default=2048, help="tokens of moe_ep (whole job)")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     rank = int(os.environ.get("RANK", "0"))
@@ -190,6 +304,10 @@ def main():
 
     if args.impl == "reference":
         run_reference_arm(args, rank)
+        return
+
+    if args.workload in ("layer_set_nshard", "moe_ep"):
+        run_sharded(args, rank, world, local)
         return
 
     import torch

@@ -1,0 +1,143 @@
+"""The multi-rank logic of the sharded forms on CPU ranks (gloo, world_size 2): row sharding + all-gather and
+expert-parallel dispatch / combine. The per-projection calls are served by the CPU oracle here (test
+infrastructure standing in for the CUDA kernels), so what is under test is the partitioning, the bucketing, the two
+all-to-alls and the un-permutation: the 2-rank result must equal the 1-rank result bit for bit."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import zero_tvm_b200 as z
+from zero_tvm_b200 import sharded
+
+
+class OracleKernels:
+    """Same interface as sharded.CudaKernels, computed by the CPU oracle on torch CPU tensors."""
+
+    def __init__(self):
+        from oracle import ztvm_oracle_c as zc
+        self.zc = zc
+
+    @staticmethod
+    def _np(t, dt=None):
+        a = t.detach().cpu().numpy()
+        return a.view(dt) if dt is not None else a
+
+    def matmul(self, y, x, W, s, b, N, K, M, out_f32=False):
+        out = self.zc.gemv_ref(self._np(x), self._np(W, np.uint32), self._np(s), self._np(b), 64, out_f32=out_f32)
+        y.copy_(torch.from_numpy(out))
+
+    def route_topk(self, ids, scores, logits, E, K, tokens):
+        i, s = self.zc.router_topk(self._np(logits), E, K, True, True)
+        ids.copy_(torch.from_numpy(i.astype(np.int32)))
+        scores.copy_(torch.from_numpy(s))
+
+    def expert_ffn(self, y_rows, x_rows, local_ids, gate, up, down, d, ffn, rows):
+        if rows == 0:
+            return
+        ids = self._np(local_ids).astype(np.uint32).reshape(rows, 1)
+        st = lambda t3: (self._np(t3[0], np.uint32), self._np(t3[1]), self._np(t3[2]))
+        gu = np.zeros((rows, 2 * ffn), dtype=np.float16)
+        self.zc.moe_gemv_ref(self._np(x_rows), *st(gate), ids, ffn, d, 64, 4, 0, 2 * ffn, d, 2 * ffn, gu.reshape(-1))
+        self.zc.moe_gemv_ref(self._np(x_rows), *st(up), ids, ffn, d, 64, 4, 0, 2 * ffn, d, 2 * ffn, gu.reshape(-1)[ffn:])
+        h = self.zc.silu_mul(gu, ffn)
+        out = np.zeros((rows, d), dtype=np.float16)
+        self.zc.moe_gemv_ref(h, *st(down), ids, d, ffn, 64, 4, ffn, d, ffn, d, out.reshape(-1))
+        y_rows.copy_(torch.from_numpy(out))
+
+    def combine(self, out, y_slots, scores, tokens, slots, d):
+        out.copy_(torch.from_numpy(self.zc.moe_combine(self._np(y_slots), self._np(scores))))
+
+
+def _t(a):
+    a = np.ascontiguousarray(a)
+    return torch.from_numpy(a.view(np.int32) if a.dtype == np.uint32 else a)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        k = OracleKernels()
+        # ---- row-sharded projection, ragged N so the last shard is short -----------------------------
+        N, K = 200, 512
+        for M in (1, 3):
+            p = z.synth.projection(N, K, M=M, seed=3)
+            lo, hi = sharded.shard_rows(N, world, rank)
+            proj = sharded.NShardedProjection(k, _t(p["W"][lo:hi]), _t(p["scales"][lo:hi]), _t(p["biases"][lo:hi]), N, K)
+            y = proj.forward(_t(p["x"]), M)
+            q.put(("nshard", M, rank, y.numpy().copy()))
+        # ---- expert-parallel MoE ------------------------------------------------------------------------
+        E, top_k, d, ffn, T = 8, 2, 256, 128, 12
+        mb = z.synth.moe_block(T, E=E, hidden=d, ffn=ffn, seed=5)
+        epr = E // world
+        sel = list(range(rank * epr, (rank + 1) * epr)) + [E]          # my routed experts + the shared one
+        stacks = {n: tuple(_t(a[sel]) for a in mb[n]) for n in ("gate", "up", "down")}
+        moe = sharded.ExpertParallelMoE(k, stacks["gate"], stacks["up"], stacks["down"], E=E, top_k=top_k, d=d, ffn=ffn)
+        tl = T // world
+        y = moe.forward(_t(mb["x"][rank * tl:(rank + 1) * tl]), _t(mb["logits"][rank * tl:(rank + 1) * tl]))
+        q.put(("moe", 0, rank, y.numpy().copy()))
+    finally:
+        dist.destroy_process_group()
+
+
+def _run(world):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    import queue as _queue
+    out = []
+    while len(out) < 3 * world:
+        try:
+            out.append(q.get(timeout=2))
+        except _queue.Empty:
+            assert all(p.exitcode in (None, 0) for p in procs), "a rank died"
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    return out
+
+
+def test_shard_rows_cover_everything():
+    for N in (1, 16, 200, 1024, 151936):
+        for G in (1, 2, 4, 8):
+            spans = [sharded.shard_rows(N, G, r) for r in range(G)]
+            assert spans[0][0] == 0 and spans[-1][1] == N
+            assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+            assert all(lo % 16 == 0 or lo == N for lo, _ in spans)
+
+
+def test_plan_dispatch_single_rank():
+    ids = torch.tensor([[3, 0], [1, 3], [2, 2]], dtype=torch.int32)
+    plan = sharded.plan_dispatch(ids, 4, 1)
+    assert plan.send_counts == [6] and sorted(plan.order.tolist()) == list(range(6))
+
+
+@pytest.mark.timeout(300)
+def test_two_ranks_equal_one_rank():
+    one = {(k, m): y for k, m, r, y in _run(1)}
+    two = _run(2)
+    for M in (1, 3):
+        for k, m, r, y in two:
+            if k == "nshard" and m == M:
+                assert np.array_equal(y.view(np.uint16), one[("nshard", M)].view(np.uint16))   # every rank holds all of y
+    ymoe = np.concatenate([y for k, m, r, y in sorted((t for t in two if t[0] == "moe"), key=lambda t: t[2])])
+    assert np.array_equal(ymoe.view(np.uint16), one[("moe", 0)].view(np.uint16))
+    # and the single-rank result is the block the oracle computes directly
+    from oracle import ztvm_oracle as zo
+    mb = z.synth.moe_block(12, E=8, hidden=256, ffn=128, seed=5)
+    ref = zo.moe_block(mb["x"], mb["logits"], mb["gate"], mb["up"], mb["down"], 8, 2, 128)["y"].astype(np.float64)
+    assert np.abs(one[("moe", 0)].astype(np.float64) - ref).max() <= 5e-3 * np.abs(ref).max()

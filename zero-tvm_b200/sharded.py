@@ -1,0 +1,172 @@
+"""Sharded forms of the path over one process per GPU (torch.distributed is the plumbing; NCCL on GPUs).
+
+The reference runs every matmul whole on one device; the two sharded forms here are the natural partitions of
+the path: output rows of a dense projection (each workgroup owns rows: src/compiler/shaders/int4_matmul.gen.ts:243)
+and experts of a MoE block (experts never mix tokens: src/zero-tvm/engine-core.ts:4444-4450).
+
+  NShardedProjection   rank r owns rows [r*N/G, (r+1)*N/G) of W / scales / biases, x is replicated; the output
+                       shards meet in one all-gather.
+  ExpertParallelMoE    rank r owns routed experts [r*E/G, (r+1)*E/G) plus a replica of the shared expert; tokens
+                       are sharded T/G; (token, slot) pairs travel to the owner of their expert in one all-to-all,
+                       the expert FFN runs there, results travel back in a second all-to-all, and the weighted
+                       combine runs where the token lives.
+
+Both classes take a `kernels` object with the per-projection calls (`CudaKernels` below binds them to the C ABI).
+The planning code (bucket, sort, permute) is device-agnostic tensor code, so the multi-rank logic is also tested on
+CPU ranks over gloo with a checker standing in for `kernels`.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+from .backend import moe_down_pod_args, moe_gate_pod_args, pod_args, resolve_matmul
+
+
+def shard_rows(N: int, world: int, rank: int) -> tuple[int, int]:
+    """Row range of rank `rank`: contiguous, sizes differ by at most one multiple of 16 rows."""
+    per = -(-N // world)
+    per = -(-per // 16) * 16
+    lo = min(N, rank * per)
+    return lo, min(N, lo + per)
+
+
+class CudaKernels:
+    """The per-projection calls of the sharded forms, bound to libztvm_b200.so on this rank's GPU."""
+
+    def __init__(self, backend):
+        self.be = backend
+
+    def matmul(self, y, x, W, s, b, N, K, M, out_f32=False):
+        entry = resolve_matmul(affine=True, K=K, out_f32=out_f32) if M == 1 else "int4_matmul_batched_dyn_affine"
+        self.be.dispatch(entry, [y, x, s, W, pod_args(K, N, m_rows=None if M == 1 else M), b])
+
+    def route_topk(self, ids, scores, logits, E, K, tokens):
+        self.be.moe_router_topk(ids, scores, logits, E, K, True, True, tokens)
+
+    def expert_ffn(self, y_rows, x_rows, local_ids, gate, up, down, d, ffn, rows):
+        """y_rows[r] = down_e(silu(gate_e x_r) * up_e x_r) with e = local_ids[r]; one slot per row."""
+        if rows == 0:
+            return
+        gu = torch.empty((rows, 1, 2 * ffn), dtype=torch.float16, device=x_rows.device)
+        h = torch.empty((rows, 1, ffn), dtype=torch.float16, device=x_rows.device)
+        ent_g = resolve_matmul(affine=True, K=d, moe=True)
+        ent_d = resolve_matmul(affine=True, K=ffn, moe=True)
+        self.be.dispatch(ent_g, [gu, x_rows, gate[1], gate[0], moe_gate_pod_args(d, ffn, 1), gate[2], local_ids], (ffn // 4, rows, 1))
+        self.be.dispatch(ent_g, [gu.view(-1)[ffn:], x_rows, up[1], up[0], moe_gate_pod_args(d, ffn, 1), up[2], local_ids], (ffn // 4, rows, 1))
+        self.be.silu_mul(h, gu, rows, ffn)
+        self.be.dispatch(ent_d, [y_rows, h, down[1], down[0], moe_down_pod_args(d, ffn, 1), down[2], local_ids], (d // 4, rows, 1))
+
+    def combine(self, out, y_slots, scores, tokens, slots, d):
+        self.be.moe_combine(out, y_slots, scores, tokens, slots, d)
+
+
+class NShardedProjection:
+    """One dense projection with its output rows split over the ranks of `group`."""
+
+    def __init__(self, kernels, W, scales, biases, N_total: int, K: int, *, out_f32: bool = False, group=None):
+        self.k, self.group = kernels, group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.N_total, self.K, self.out_f32 = N_total, K, out_f32
+        self.lo, self.hi = shard_rows(N_total, self.world, self.rank)
+        self.per = shard_rows(N_total, self.world, 0)[1]
+        assert W.shape[0] == self.hi - self.lo, "pass this rank's row shard"
+        self.W, self.s, self.b = W, scales, biases
+
+    def forward(self, x: torch.Tensor, M: int) -> torch.Tensor:
+        """x f16 [M, K] (replicated) -> y [M, N_total], every rank holding the whole output."""
+        dt = torch.float32 if self.out_f32 else torch.float16
+        n_loc = self.hi - self.lo
+        # every rank contributes a [M, per] block (the last shard may be short: padded, trimmed after the gather)
+        y_loc = torch.zeros((M, self.per), dtype=dt, device=x.device)
+        if n_loc:
+            if n_loc == self.per:
+                self.k.matmul(y_loc, x, self.W, self.s, self.b, n_loc, self.K, M, self.out_f32)
+            else:
+                tmp = torch.empty((M, n_loc), dtype=dt, device=x.device)
+                self.k.matmul(tmp, x, self.W, self.s, self.b, n_loc, self.K, M, self.out_f32)
+                y_loc[:, :n_loc] = tmp
+        if self.world == 1:
+            return y_loc[:, :self.N_total]
+        buf = torch.empty((self.world * M, self.per), dtype=dt, device=x.device)   # rank-major concatenation
+        dist.all_gather_into_tensor(buf, y_loc, group=self.group)
+        return buf.view(self.world, M, self.per).permute(1, 0, 2).reshape(M, self.world * self.per)[:, :self.N_total]
+
+
+@dataclass
+class DispatchPlan:
+    order: torch.Tensor        # [P] pair indices (token*K + slot) sorted by destination rank
+    send_counts: list          # pairs per destination rank
+    recv_counts: list          # pairs arriving from each source rank
+    local_expert: torch.Tensor  # [P] expert index inside the destination's stack, in send order
+
+
+def plan_dispatch(ids_routed: torch.Tensor, experts_per_rank: int, world: int, group=None) -> DispatchPlan:
+    """Buckets the routed (token, slot) pairs by the rank that owns their expert."""
+    flat = ids_routed.reshape(-1).to(torch.int64)
+    dest = torch.div(flat, experts_per_rank, rounding_mode="floor")
+    order = torch.argsort(dest, stable=True)
+    send = torch.bincount(dest, minlength=world)[:world]
+    if world > 1:
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=group)
+    else:
+        recv = send.clone()
+    return DispatchPlan(order, send.tolist(), recv.tolist(), (flat[order] % experts_per_rank).to(torch.int32))
+
+
+class ExpertParallelMoE:
+    """Expert-parallel form of the block the engine runs as seven dispatches (engine-core.ts:2342-2349)."""
+
+    def __init__(self, kernels, gate, up, down, *, E: int, top_k: int, d: int, ffn: int, group=None):
+        """gate / up / down: (W, scales, biases) stacks of THIS rank: E/G routed experts followed by the shared one."""
+        self.k, self.group = kernels, group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        assert E % self.world == 0
+        self.E, self.top_k, self.d, self.ffn = E, top_k, d, ffn
+        self.epr = E // self.world
+        self.gate, self.up, self.down = gate, up, down
+
+    def _a2a(self, send: torch.Tensor, send_counts, recv_counts) -> torch.Tensor:
+        out = torch.empty((sum(recv_counts),) + tuple(send.shape[1:]), dtype=send.dtype, device=send.device)
+        if self.world == 1:
+            out.copy_(send)
+        else:
+            dist.all_to_all_single(out, send, output_split_sizes=recv_counts, input_split_sizes=send_counts, group=self.group)
+        return out
+
+    def forward(self, x: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
+        """x f16 [T_local, d], logits f32 [T_local, E+1] -> y f16 [T_local, d]."""
+        T, K, d = x.shape[0], self.top_k, self.d
+        dev = x.device
+        ids = torch.empty((T, K + 1), dtype=torch.int32, device=dev)
+        scores = torch.empty((T, K + 1), dtype=torch.float32, device=dev)
+        self.k.route_topk(ids, scores, logits, self.E, K, T)
+        plan = plan_dispatch(ids[:, :K], self.epr, self.world, self.group)
+        # dispatch: activation rows and their local expert index, in destination order
+        tok_of_pair = torch.div(plan.order, K, rounding_mode="floor")
+        x_send = x.index_select(0, tok_of_pair)
+        x_recv = self._a2a(x_send, plan.send_counts, plan.recv_counts)
+        e_recv = self._a2a(plan.local_expert.reshape(-1, 1), plan.send_counts, plan.recv_counts)
+        # expert FFN on what arrived
+        R = x_recv.shape[0]
+        y_recv = torch.empty((R, d), dtype=torch.float16, device=dev)
+        self.k.expert_ffn(y_recv, x_recv, e_recv.contiguous(), self.gate, self.up, self.down, d, self.ffn, R)
+        # combine: results travel back and are un-permuted into [T, K+1, d]
+        y_back = self._a2a(y_recv, plan.recv_counts, plan.send_counts)
+        y_slots = torch.empty((T, K + 1, d), dtype=torch.float16, device=dev)
+        routed = torch.empty((T * K, d), dtype=torch.float16, device=dev)
+        routed.index_copy_(0, plan.order, y_back)
+        y_slots[:, :K] = routed.view(T, K, d)
+        # the shared expert is replicated: its slot is computed where the token lives
+        y_sh = torch.empty((T, d), dtype=torch.float16, device=dev)
+        shared_idx = torch.full((T, 1), self.epr, dtype=torch.int32, device=dev)
+        self.k.expert_ffn(y_sh, x, shared_idx, self.gate, self.up, self.down, d, self.ffn, T)
+        y_slots[:, K] = y_sh
+        out = torch.empty((T, d), dtype=torch.float16, device=dev)
+        self.k.combine(out, y_slots, scores, T, K + 1, d)
+        return out
