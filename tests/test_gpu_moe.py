@@ -47,15 +47,18 @@ def check_block(got, mb, oracle_c, K_top=8, bits=4):
     # routing: indices exact, scores 2e-6 (tests/kernels/run.mjs:333-336)
     assert np.array_equal(got["ids"], ids_ref)
     assert np.abs(got["scores"] - sc_ref).max() < 2e-6
-    # each stage against the f64 anchor computed from the GPU's own (already checked) inputs
-    g64 = oracle_c.moe_matmul_f64(mb["x"], *mb["gate"], ids_ref, ffn, d, 64, bits, in_per_slot=False)
-    u64 = oracle_c.moe_matmul_f64(mb["x"], *mb["up"], ids_ref, ffn, d, 64, bits, in_per_slot=False)
-    assert zo.rel_err_scaled(got["gate_up"][..., :ffn], g64) <= TOL
-    assert zo.rel_err_scaled(got["gate_up"][..., ffn:], u64) <= TOL
+    # each stage against the f64 anchor computed from the GPU's own (already checked) inputs. From 128 (token, slot)
+    # pairs on, 4-bit experts run as a grouped tensor-core GEMM: f16 weights (anchor over W16) and the GEMM floor.
+    grouped = bits == 4 and ids_ref.size >= 128 and ffn % 128 == 0 and d % 128 == 0
+    frac = 1e-2 if grouped else 1e-3
+    g64 = oracle_c.moe_matmul_f64(mb["x"], *mb["gate"], ids_ref, ffn, d, 64, bits, in_per_slot=False, w16=grouped)
+    u64 = oracle_c.moe_matmul_f64(mb["x"], *mb["up"], ids_ref, ffn, d, 64, bits, in_per_slot=False, w16=grouped)
+    assert zo.rel_err_scaled(got["gate_up"][..., :ffn], g64, frac) <= TOL
+    assert zo.rel_err_scaled(got["gate_up"][..., ffn:], u64, frac) <= TOL
     h_ref = oracle_c.silu_mul(got["gate_up"], ffn)
     assert zo.rel_err_scaled(got["h"], h_ref.astype(np.float64)) <= TOL
-    d64 = oracle_c.moe_matmul_f64(got["h"], *mb["down"], ids_ref, d, ffn, 64, bits, in_per_slot=True)
-    assert zo.rel_err_scaled(got["y_slots"], d64) <= TOL
+    d64 = oracle_c.moe_matmul_f64(got["h"], *mb["down"], ids_ref, d, ffn, 64, bits, in_per_slot=True, w16=grouped)
+    assert zo.rel_err_scaled(got["y_slots"], d64, frac) <= TOL
     y_ref = oracle_c.moe_combine(got["y_slots"], got["scores"])
     assert np.array_equal(got["y"].view(np.uint16), y_ref.view(np.uint16))
     assert np.isfinite(got["y"].astype(np.float32)).all()
@@ -142,6 +145,27 @@ def test_bad_expert_id_is_counted_not_followed(backend, dev):
     assert (got[0, 1, :128] == 7.0).all()          # skipped pair untouched
     assert (got[0, 0, :128] != 7.0).any()
     assert backend.ctx.device_errors() == 0        # counter resets
+
+
+def test_grouped_path_handles_bad_ids_and_matches_per_pair_path(backend, dev, oracle_c):
+    """160 pairs go through the grouped GEMM: an out-of-range id is counted and its row left untouched; every other
+    row agrees with the f64 anchor."""
+    mb = z.synth.moe_block(32, E=8, hidden=256, ffn=128, seed=6)
+    slots = 5
+    rng = np.random.default_rng(0)
+    ids = rng.integers(0, 9, size=(32, slots), dtype=np.uint32)
+    ids[3, 2] = 77                                     # out of range
+    out = dev.empty((32, slots, 2 * 128), np.float16, fill=7.0)
+    gw, gs, gb = (dev.put(a) for a in mb["gate"])
+    backend.dispatch("int4_matmul_tiled_vec4h_affine_moe",
+                     [out, dev.put(mb["x"]), gs, gw, moe_gate_pod_args(256, 128, slots), gb, dev.put(ids)], (32, 32, slots))
+    assert backend.ctx.device_errors() == 1
+    got = dev.get(out)
+    assert (got[3, 2, :128] == 7.0).all() and (got[..., 128:] == 7.0).all()
+    ids_ok = ids.copy(); ids_ok[3, 2] = 0
+    ref = oracle_c.moe_matmul_f64(mb["x"], *mb["gate"], ids_ok, 128, 256, 64, 4, in_per_slot=False, w16=True)
+    mask = np.ones((32, slots), bool); mask[3, 2] = False
+    assert zo.rel_err_scaled(got[..., :128][mask], ref[mask], 1e-2) <= TOL
 
 
 def test_moe_argument_errors(backend, dev):

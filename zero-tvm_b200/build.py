@@ -16,8 +16,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "libztvm_b200.so")
-SOURCES = ["ztvm_api.cu", "ztvm_gemv.cu", "ztvm_gemv_mma.cu", "ztvm_gemm.cu", "ztvm_glue.cu"]
-HEADERS = ["ztvm_device.cuh", "ztvm_kernels.h", os.path.join("..", "..", "include", "ztvm_b200.h")]
+SOURCES = ["ztvm_api.cu", "ztvm_gemv.cu", "ztvm_gemv_mma.cu", "ztvm_gemm.cu", "ztvm_moe_gemm.cu", "ztvm_glue.cu"]
+HEADERS = ["ztvm_device.cuh", "ztvm_tc.cuh", "ztvm_kernels.h", os.path.join("..", "..", "include", "ztvm_b200.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
@@ -44,7 +44,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not _stale():
         return LIB
     os.makedirs(LIB_DIR, exist_ok=True)
-    flags = [f for f in NVCC_FLAGS if f != "--use_fast_math=false"]
+    flags = [f for f in NVCC_FLAGS if f != "--use_fast_math=false"] + os.environ.get("ZTVM_NVCC_EXTRA", "").split()
     objs = []
     procs = []
     for s in SOURCES:

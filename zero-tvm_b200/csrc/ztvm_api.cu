@@ -21,6 +21,10 @@ struct ztvm_ctx {
   void* h_pinned; size_t h_pinned_bytes;
   void* d_x; size_t d_x_bytes;
   void* d_y; size_t d_y_bytes;
+  // plan scratch of the grouped MoE matmul (grown on demand: a call that needs more synchronises the device,
+  // reallocates and goes on; make one call at the largest size before capturing a graph)
+  void* d_ws; size_t d_ws_bytes;
+  int moe_grouped;  // env ZTVM_MOE_GROUPED=0|1 forces the per-pair GEMV / the grouped GEMM (a measurement knob)
 };
 
 namespace {
@@ -175,6 +179,8 @@ ztvm_status ztvm_init(int32_t device_ordinal, ztvm_ctx** out_ctx) {
   }
   const char* ng = getenv("ZTVM_NO_GEMM");
   c->no_gemm = (ng && ng[0] == '1') ? 1 : 0;
+  const char* mg = getenv("ZTVM_MOE_GROUPED");
+  c->moe_grouped = !mg ? -1 : (mg[0] == '1' ? 1 : 0);
   const char* gp = getenv("ZTVM_GEMV_PATH");
   c->gemv_path = !gp ? 0 : !strcmp(gp, "fma") ? 1 : !strcmp(gp, "mma") ? 2 : 0;
   c->magic = kMagic;
@@ -189,6 +195,7 @@ ztvm_status ztvm_destroy(ztvm_ctx* ctx) {
   if (ctx->h_pinned) cudaFreeHost(ctx->h_pinned);
   if (ctx->d_x) cudaFree(ctx->d_x);
   if (ctx->d_y) cudaFree(ctx->d_y);
+  if (ctx->d_ws) cudaFree(ctx->d_ws);
   cudaFree(ctx->err_counter);
   cudaStreamDestroy(ctx->stream);
   ctx->magic = 0;
@@ -273,6 +280,26 @@ ztvm_status ztvm_int4_matmul_moe(ztvm_ctx* ctx, const ztvm_moe_desc* md, void* y
   cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : ctx->stream;
   ztvm_mm_desc dd = *d;
   dd.M = 1;
+  // Many pairs: sort them by expert and run tensor-core tiles (each expert's weights dequantised once per 128 pairs).
+  const uint64_t pairs = (uint64_t)md->tokens * md->slots;
+  const bool want_grouped = ctx->moe_grouped < 0 ? pairs >= 128 : ctx->moe_grouped == 1;
+  if (want_grouped && pairs < (1ull << 31) && (md->out_slot_stride | md->out_tok_stride) % 8 == 0 && aligned(y, 16) &&
+      ztvm::moe_grouped_supported((int)d->bits, d->group, d->K, d->N, md->experts)) {
+    const size_t need = ztvm::moe_grouped_scratch_bytes(md->experts, (uint32_t)pairs);
+    if (ctx->d_ws_bytes < need) {
+      ZTVM_CUDA(cudaDeviceSynchronize());
+      if ((s = grow(&ctx->d_ws, &ctx->d_ws_bytes, need, false))) return s;
+    }
+    ztvm::GemvParams p = gemv_params(&dd, y, x, scales, packed_w, biases);
+    p.ids = ids;
+    p.experts = md->experts;
+    p.in_slot_stride = md->in_slot_stride; p.out_slot_stride = md->out_slot_stride;
+    p.in_tok_stride = md->in_tok_stride; p.out_tok_stride = md->out_tok_stride;
+    p.ids_stride = md->ids_stride;
+    p.err_counter = ctx->err_counter;
+    ZTVM_CUDA(ztvm::launch_moe_grouped(p, md->tokens, md->slots, static_cast<uint32_t*>(ctx->d_ws), ctx->err_counter + 1, st));
+    return ZTVM_OK;
+  }
   // grid.y carries the token: split very long token lists into slabs of 65535
   for (uint32_t t0 = 0; t0 < md->tokens; t0 += 65535) {
     const uint32_t nt = md->tokens - t0 < 65535 ? md->tokens - t0 : 65535;

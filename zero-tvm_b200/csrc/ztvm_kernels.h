@@ -38,6 +38,13 @@ bool gemm_w4_supported(int bits, uint32_t group, uint32_t K);
 cudaError_t launch_gemm_w4(const uint32_t* W, const __half* S, const __half* B, const __half* X, void* Y, uint32_t M,
                            uint32_t N, uint32_t K, uint32_t group_shift, bool out_f32, uint32_t* status, cudaStream_t st);
 
+// Grouped MoE expert matmul (ztvm_moe_gemm.cu): pairs sorted by expert, tcgen05 tiles. `scratch` holds the plan
+// (moe_grouped_scratch_bytes), `status[0]` receives a non-zero code if a bounded wait ran out.
+size_t moe_grouped_scratch_bytes(uint32_t experts, uint32_t pairs);
+bool moe_grouped_supported(int bits, uint32_t group, uint32_t K, uint32_t N, uint32_t experts);
+cudaError_t launch_moe_grouped(const GemvParams& g, uint32_t tokens, uint32_t slots, uint32_t* scratch, uint32_t* status,
+                               cudaStream_t st);
+
 cudaError_t launch_unpack_codes(const uint32_t* W, uint8_t* codes, uint32_t N, uint32_t K, int bits, cudaStream_t st);
 cudaError_t launch_dequant(const uint32_t* W, const __half* S, const __half* B, void* out, uint32_t N, uint32_t K,
                            int bits, uint32_t group_shift, bool affine, bool as_f16, cudaStream_t st);
