@@ -60,6 +60,9 @@ class Dev:
         t = torch.empty(shape, dtype=tdt, device="cuda")
         if fill is not None:
             t.fill_(fill)
+            # the fill runs on torch's stream and the library launches on its own: order them here, or a late fill
+            # could overwrite what a kernel has already written
+            torch.cuda.synchronize()
         return t
 
     @staticmethod

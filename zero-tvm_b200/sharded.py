@@ -34,33 +34,46 @@ def shard_rows(N: int, world: int, rank: int) -> tuple[int, int]:
 
 
 class CudaKernels:
-    """The per-projection calls of the sharded forms, bound to libztvm_b200.so on this rank's GPU."""
+    """The per-projection calls of the sharded forms, bound to libztvm_b200.so on this rank's GPU.
+
+    Every call is issued on torch's CURRENT stream, the one the surrounding tensor code and the NCCL collectives
+    are ordered on; the library's own stream is non-blocking and would race with them.
+    """
 
     def __init__(self, backend):
         self.be = backend
 
+    @staticmethod
+    def _stream() -> int:
+        h = torch.cuda.current_stream().cuda_stream
+        return h if h else 1      # 0 would mean "the library's stream" to the C ABI; 1 is the legacy default stream
+
     def matmul(self, y, x, W, s, b, N, K, M, out_f32=False):
         entry = resolve_matmul(affine=True, K=K, out_f32=out_f32) if M == 1 else "int4_matmul_batched_dyn_affine"
-        self.be.dispatch(entry, [y, x, s, W, pod_args(K, N, m_rows=None if M == 1 else M), b])
+        self.be.dispatch(entry, [y, x, s, W, pod_args(K, N, m_rows=None if M == 1 else M), b], stream=self._stream())
 
     def route_topk(self, ids, scores, logits, E, K, tokens):
-        self.be.moe_router_topk(ids, scores, logits, E, K, True, True, tokens)
+        self.be.moe_router_topk(ids, scores, logits, E, K, True, True, tokens, stream=self._stream())
 
     def expert_ffn(self, y_rows, x_rows, local_ids, gate, up, down, d, ffn, rows):
         """y_rows[r] = down_e(silu(gate_e x_r) * up_e x_r) with e = local_ids[r]; one slot per row."""
         if rows == 0:
             return
+        st = self._stream()
         gu = torch.empty((rows, 1, 2 * ffn), dtype=torch.float16, device=x_rows.device)
         h = torch.empty((rows, 1, ffn), dtype=torch.float16, device=x_rows.device)
         ent_g = resolve_matmul(affine=True, K=d, moe=True)
         ent_d = resolve_matmul(affine=True, K=ffn, moe=True)
-        self.be.dispatch(ent_g, [gu, x_rows, gate[1], gate[0], moe_gate_pod_args(d, ffn, 1), gate[2], local_ids], (ffn // 4, rows, 1))
-        self.be.dispatch(ent_g, [gu.view(-1)[ffn:], x_rows, up[1], up[0], moe_gate_pod_args(d, ffn, 1), up[2], local_ids], (ffn // 4, rows, 1))
-        self.be.silu_mul(h, gu, rows, ffn)
-        self.be.dispatch(ent_d, [y_rows, h, down[1], down[0], moe_down_pod_args(d, ffn, 1), down[2], local_ids], (d // 4, rows, 1))
+        self.be.dispatch(ent_g, [gu, x_rows, gate[1], gate[0], moe_gate_pod_args(d, ffn, 1), gate[2], local_ids],
+                         (ffn // 4, rows, 1), stream=st)
+        self.be.dispatch(ent_g, [gu.view(-1)[ffn:], x_rows, up[1], up[0], moe_gate_pod_args(d, ffn, 1), up[2], local_ids],
+                         (ffn // 4, rows, 1), stream=st)
+        self.be.silu_mul(h, gu, rows, ffn, stream=st)
+        self.be.dispatch(ent_d, [y_rows, h, down[1], down[0], moe_down_pod_args(d, ffn, 1), down[2], local_ids],
+                         (d // 4, rows, 1), stream=st)
 
     def combine(self, out, y_slots, scores, tokens, slots, d):
-        self.be.moe_combine(out, y_slots, scores, tokens, slots, d)
+        self.be.moe_combine(out, y_slots, scores, tokens, slots, d, stream=self._stream())
 
 
 class NShardedProjection:
