@@ -17,6 +17,9 @@
  *  - Buffer arguments are device addresses (what cudaMalloc returns). The library never
  *    allocates or frees caller buffers. Unless stated otherwise a call is asynchronous on
  *    `stream` (a cudaStream_t; NULL = the context's own stream) and performs no host sync.
+ *    The context's own stream is non-blocking: it is NOT ordered against the legacy default stream.
+ *    A caller whose other work runs on the legacy default stream passes cudaStreamLegacy (handle 1),
+ *    not NULL, to have the call ordered with that work.
  *  - Layouts: packed weights u32[N][K*bits/32], 4-bit code i of a word at bits [4i,4i+4)
  *    (src/compiler/shaders/int4_matmul.gen.ts:157-167); 3-bit code i of a row at bit 3i of the
  *    row's LSB-first bitstream (int4_matmul.gen.ts:115-131); scales / biases f16[N][K/group];
@@ -116,6 +119,27 @@ typedef struct ztvm_moe_desc {
 ZTVM_API ztvm_status ztvm_int4_matmul_moe(ztvm_ctx* ctx, const ztvm_moe_desc* desc, void* y, const void* x,
                                  const void* scales, const void* packed_w, const void* biases,
                                  const uint32_t* ids, void* stream);
+
+/* ztvm_int4_matmul_moe for callers that must not let the call allocate. It has no counterpart in the reference
+ * (WebGPU buffers are all created up front there); it exists for hosts whose device memory is entirely handed
+ * to their own pool, or whose serving loop cannot take the device-wide synchronisation that growing a work
+ * buffer costs. ztvm_int4_matmul_moe keeps its plan (expert histogram, tile table, sorted pair list) in a
+ * buffer that grows on demand; this entry point keeps it in a fixed array inside the library's device image
+ * and makes no allocating call at all.
+ *  - Limits: tokens*slots <= ZTVM_MOE_NOALLOC_MAX_PAIRS and experts <= ZTVM_MOE_NOALLOC_MAX_EXPERTS, else
+ *    ZTVM_ERR_TOO_LARGE. Only the tensor-core form runs here: bits 4, group 64, K % 64 == 0, N % 128 == 0,
+ *    strides multiples of 8 elements, y 16-byte aligned; anything else is ZTVM_ERR_UNSUPPORTED /
+ *    ZTVM_ERR_ALIGNMENT (there is no fall-back to the per-pair kernel). Results are those of
+ *    ztvm_int4_matmul_moe on the same inputs, bit for bit.
+ *  - The first call on a device looks up the array's device address and loads the kernels: make one call
+ *    per device at start-up, before any stream capture.
+ *  - There is ONE array per device, shared by every context and stream: two calls that overlap in time on
+ *    the same device race on it. Issue them on one stream, or order them with events. */
+#define ZTVM_MOE_NOALLOC_MAX_PAIRS 65536u
+#define ZTVM_MOE_NOALLOC_MAX_EXPERTS 1024u
+ZTVM_API ztvm_status ztvm_int4_matmul_moe_noalloc(ztvm_ctx* ctx, const ztvm_moe_desc* desc, void* y, const void* x,
+                                         const void* scales, const void* packed_w, const void* biases,
+                                         const uint32_t* ids, void* stream);
 
 /* softmax over E routed experts -> top-K (ties to the lower index) -> optional renormalisation ->
  * slot K = expert E with sigmoid(logit[E]) when has_shared. logits f32[tokens][E+has_shared] ->

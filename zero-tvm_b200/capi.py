@@ -14,7 +14,8 @@ LIB_PATH = os.path.join(_HERE, "lib", "libztvm_b200.so")
 # every symbol include/ztvm_b200.h declares
 SYMBOLS = [
     "ztvm_version", "ztvm_status_string", "ztvm_init", "ztvm_destroy", "ztvm_last_error", "ztvm_sync",
-    "ztvm_int4_matmul", "ztvm_int4_matmul_host", "ztvm_int4_matmul_moe", "ztvm_moe_route_topk", "ztvm_silu_mul",
+    "ztvm_int4_matmul", "ztvm_int4_matmul_host", "ztvm_int4_matmul_moe", "ztvm_int4_matmul_moe_noalloc",
+    "ztvm_moe_route_topk", "ztvm_silu_mul",
     "ztvm_moe_combine", "ztvm_unpack_codes", "ztvm_dequant", "ztvm_device_errors",
 ]
 
@@ -62,6 +63,7 @@ def load() -> C.CDLL:
         "ztvm_int4_matmul": [vp, C.POINTER(MmDesc), vp, vp, vp, vp, vp, vp],
         "ztvm_int4_matmul_host": [vp, C.POINTER(MmDesc), vp, vp, vp, vp, vp],
         "ztvm_int4_matmul_moe": [vp, C.POINTER(MoeDesc), vp, vp, vp, vp, vp, vp, vp],
+        "ztvm_int4_matmul_moe_noalloc": [vp, C.POINTER(MoeDesc), vp, vp, vp, vp, vp, vp, vp],
         "ztvm_moe_route_topk": [vp, u32, u32, u32, u32, u32, vp, vp, vp, vp],
         "ztvm_silu_mul": [vp, u32, u32, vp, vp, vp],
         "ztvm_moe_combine": [vp, u32, u32, u32, vp, vp, vp, vp],
@@ -139,6 +141,11 @@ class Context:
     def int4_matmul_moe(self, desc: MoeDesc, y, x, scales, packed_w, biases, ids, stream=None):
         check(self._lib.ztvm_int4_matmul_moe(self.handle, C.byref(desc), ptr(y), ptr(x), ptr(scales),
                                              ptr(packed_w), ptr(biases), ptr(ids), stream_ptr(stream)))
+
+    def int4_matmul_moe_noalloc(self, desc: MoeDesc, y, x, scales, packed_w, biases, ids, stream=None):
+        """The grouped MoE matmul with its plan in a fixed device array (no allocation; limits in the header)."""
+        check(self._lib.ztvm_int4_matmul_moe_noalloc(self.handle, C.byref(desc), ptr(y), ptr(x), ptr(scales),
+                                                     ptr(packed_w), ptr(biases), ptr(ids), stream_ptr(stream)))
 
     def moe_route_topk(self, E, K, norm_topk, has_shared, tokens, ids, scores, logits, stream=None):
         check(self._lib.ztvm_moe_route_topk(self.handle, E, K, int(norm_topk), int(has_shared), tokens, ptr(ids),

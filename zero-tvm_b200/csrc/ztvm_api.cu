@@ -318,6 +318,49 @@ ztvm_status ztvm_int4_matmul_moe(ztvm_ctx* ctx, const ztvm_moe_desc* md, void* y
   return ZTVM_OK;
 }
 
+ztvm_status ztvm_int4_matmul_moe_noalloc(ztvm_ctx* ctx, const ztvm_moe_desc* md, void* y, const void* x,
+                                         const void* scales, const void* packed_w, const void* biases,
+                                         const uint32_t* ids, void* stream) {
+  ztvm_status s = check_ctx(ctx);   // also makes the context's device current: the scratch array is per device
+  if (s) return s;
+  if (!md) return fail(ZTVM_ERR_NULL_POINTER, "desc is NULL");
+  const ztvm_mm_desc* d = &md->mm;
+  if ((s = check_desc(d, false))) return s;
+  if (!d->affine) return fail(ZTVM_ERR_UNSUPPORTED, "MoE expert weights are affine-quantised only");
+  if (d->out_f32) return fail(ZTVM_ERR_UNSUPPORTED, "MoE expert matmuls write f16");
+  if (d->M > 1) return fail(ZTVM_ERR_BAD_DIMS, "MoE matmul is per (token, slot): mm.M must be 1 (or 0)");
+  if ((s = check_buffers(d, y, x, scales, packed_w, biases))) return s;
+  if (!ids) return fail(ZTVM_ERR_NULL_POINTER, "ids is NULL");
+  if (md->tokens == 0) return ZTVM_OK;
+  if (md->slots == 0 || md->experts == 0) return fail(ZTVM_ERR_BAD_DIMS, "slots and experts must be non-zero");
+  if (md->ids_stride < md->slots) return fail(ZTVM_ERR_BAD_DIMS, "ids_stride=%u < slots=%u", md->ids_stride, md->slots);
+  const uint64_t pairs = (uint64_t)md->tokens * md->slots;
+  if (!ztvm::moe_static_scratch_fits(md->experts, pairs))
+    return fail(ZTVM_ERR_TOO_LARGE,
+                "tokens*slots=%llu, experts=%u exceed the fixed scratch of this entry point (at most %u pairs, %u experts): "
+                "split the token list or call ztvm_int4_matmul_moe",
+                (unsigned long long)pairs, md->experts, (unsigned)ZTVM_MOE_NOALLOC_MAX_PAIRS,
+                (unsigned)ZTVM_MOE_NOALLOC_MAX_EXPERTS);
+  if (!ztvm::moe_grouped_supported((int)d->bits, d->group, d->K, d->N, md->experts))
+    return fail(ZTVM_ERR_UNSUPPORTED,
+                "this entry point runs the tensor-core tiles only: bits=4, group=64, K %% 64 == 0, N %% 128 == 0 "
+                "(got bits=%u group=%u K=%u N=%u)", d->bits, d->group, d->K, d->N);
+  if ((md->in_slot_stride | md->in_tok_stride | md->out_slot_stride | md->out_tok_stride) % 8 || !aligned(y, 16))
+    return fail(ZTVM_ERR_ALIGNMENT, "strides must be multiples of 8 elements and y 16-byte aligned");
+  cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : ctx->stream;
+  ztvm_mm_desc dd = *d;
+  dd.M = 1;
+  ztvm::GemvParams p = gemv_params(&dd, y, x, scales, packed_w, biases);
+  p.ids = ids;
+  p.experts = md->experts;
+  p.in_slot_stride = md->in_slot_stride; p.out_slot_stride = md->out_slot_stride;
+  p.in_tok_stride = md->in_tok_stride; p.out_tok_stride = md->out_tok_stride;
+  p.ids_stride = md->ids_stride;
+  p.err_counter = ctx->err_counter;
+  ZTVM_CUDA(ztvm::launch_moe_grouped_static(p, md->tokens, md->slots, ctx->err_counter + 1, st));
+  return ZTVM_OK;
+}
+
 ztvm_status ztvm_moe_route_topk(ztvm_ctx* ctx, uint32_t E, uint32_t K, uint32_t norm_topk, uint32_t has_shared,
                                 uint32_t tokens, uint32_t* ids, float* scores, const float* logits, void* stream) {
   ztvm_status s = check_ctx(ctx);

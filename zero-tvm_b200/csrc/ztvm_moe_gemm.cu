@@ -8,6 +8,8 @@
 // GEMM (one CTA per tile x 128 weight rows): warp 0 TMA-loads the expert's packed weights, warp 1 issues
 // tcgen05.mma, warps 2..9 gather the activation rows of the tile's pairs with 16-byte cp.async straight into
 // the swizzled A slot, dequantise the B slot, and at the end scatter the rows of D to where each pair lives.
+#include <mutex>
+
 #include "ztvm_kernels.h"
 #include "ztvm_tc.cuh"
 
@@ -378,6 +380,54 @@ cudaError_t launch_moe_grouped(const GemvParams& g, uint32_t tokens, uint32_t sl
   dim3 grid(g.N / kMoeBN, max_tiles);
   moe_gemm_w4_kernel<<<grid, kMoeThreads, smem, st>>>(tmap_w, p);
   return cudaGetLastError();
+}
+
+// ---- the same matmul with its planning scratch in a fixed device array: nothing is allocated ------------------
+// For callers that cannot let a matmul allocate: a serving loop whose device memory is all handed to its own pool,
+// or one that cannot afford the device-wide synchronisation that growing a buffer implies. The scratch lives in the
+// module's own image, so it exists (once per device) as soon as the module is loaded there.
+constexpr uint32_t kMoeStaticMaxExperts = 1024, kMoeStaticMaxPairs = 65536;
+constexpr size_t kMoeStaticWords = (size_t)kMoeStaticMaxExperts * 3 + 2 + 2 +
+                                   ((size_t)(kMoeStaticMaxPairs + kMoeBM - 1) / kMoeBM + kMoeStaticMaxExperts) * 3 +
+                                   kMoeStaticMaxPairs + 16;   // = moe_scratch_words(max experts, max pairs), 293 KB
+static __device__ __align__(256) uint32_t g_moe_static_scratch[kMoeStaticWords];
+
+bool moe_static_scratch_fits(uint32_t experts, uint64_t pairs) {
+  return experts <= kMoeStaticMaxExperts && pairs <= kMoeStaticMaxPairs &&
+         moe_scratch_words(experts, (uint32_t)pairs) <= kMoeStaticWords;
+}
+
+// Device address of the array on the CURRENT device. The host-side name of a __device__ array is not a device
+// address: the runtime has to be asked for it, once per device (each device holds its own copy of the array).
+static cudaError_t moe_static_scratch_ptr(uint32_t** out) {
+  constexpr int kMaxDevices = 64;
+  static uint32_t* ptrs[kMaxDevices] = {};
+  static std::mutex mu;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!ptrs[dev]) {
+    void* addr = nullptr;
+    e = cudaGetSymbolAddress(&addr, g_moe_static_scratch);
+    if (e != cudaSuccess) return e;
+    if (!addr) return cudaErrorInvalidSymbol;
+    ptrs[dev] = static_cast<uint32_t*>(addr);
+  }
+  *out = ptrs[dev];
+  return cudaSuccess;
+}
+
+cudaError_t launch_moe_grouped_static(const GemvParams& g, uint32_t tokens, uint32_t slots, uint32_t* status,
+                                      cudaStream_t st) {
+  if (!moe_static_scratch_fits(g.experts, (uint64_t)tokens * slots)) return cudaErrorInvalidValue;
+  uint32_t* scratch = nullptr;
+  const cudaError_t e = moe_static_scratch_ptr(&scratch);
+  if (e != cudaSuccess) return e;
+  // launch_moe_grouped zeroes the words that must start at zero (counts, offsets, cursors, tile count) on `st`
+  // before the planning kernels; the rest of the scratch is fully written before it is read.
+  return launch_moe_grouped(g, tokens, slots, scratch, status, st);
 }
 
 }  // namespace ztvm
