@@ -11,6 +11,7 @@ Workloads
   prefill_gemm_m512  X[512,2048] f16 times int4 W[8192,2048] (group 64, affine), f16 out. TFLOP/s. (default)
   decode_gemv        x[1,2048] times the same weight format, GB/s of algorithmic bytes.
   decode_layer_set   the 8B-class projections at M=1 (q,k,v,o,gate,up,down,lm_head), GB/s.
+  shape:NxKxM[xf32]  one projection of any size (GB/s for M <= 8, TFLOP/s above); used for profiles and sweeps.
 
   layer_set_nshard   the same eight projections with their output rows sharded over the ranks and one all-gather
                      per projection (strong scaling, GB/s of the whole layer set); --m-rows 1|4
@@ -109,6 +110,11 @@ def workload_shapes(name):
         return [("W[8192,2048] M=1", 8192, 2048, 1, False)]
     if name == "decode_layer_set":
         return [(n, N, K, 1, f32) for n, N, K, f32 in z.synth.DENSE_LAYER_SET]
+    if name.startswith("shape:"):      # shape:NxKxM (f16 out) or shape:NxKxMxf32 — any one projection, e.g. for profiling
+        parts = name[6:].split("x")
+        N, K, M = (int(v) for v in parts[:3])
+        f32 = len(parts) > 3 and parts[3] == "f32"
+        return [(f"W[{N},{K}] M={M}", N, K, M, f32)]
     raise SystemExit(f"unknown workload {name}")
 
 

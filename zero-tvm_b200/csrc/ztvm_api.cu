@@ -12,7 +12,10 @@
 struct ztvm_ctx {
   uint32_t magic;
   int no_gemm;    // env ZTVM_NO_GEMM=1: keep M > 8 on GEMV slabs (a measurement knob)
-  int gemv_path;  // 0 auto: M = 1 on the CUDA-core FMA GEMV, M = 2..8 on the matrix-unit GEMV; 1: FMA always; 2: matrix unit always (env ZTVM_GEMV_PATH=fma|mma, a measurement knob)
+  // 0 auto: the persistent matrix-unit GEMV where its shape rules allow, else M = 1 on the CUDA-core FMA GEMV and
+  // M = 2..8 on the tiled matrix-unit GEMV; 1: FMA always; 2: tiled matrix unit always; 3: like 0 but M = 1 stays on
+  // the FMA GEMV (env ZTVM_GEMV_PATH=fma|mma|tc|tc_m2, a measurement knob)
+  int gemv_path;
   int device;
   int sm_count;
   cudaStream_t stream;
@@ -84,7 +87,7 @@ ztvm_status check_desc(const ztvm_mm_desc* d, bool need_m) {
 
 bool use_mma(const ztvm_ctx* ctx, const ztvm_mm_desc* d, uint32_t m) {
   if (!ztvm::gemv_mma_supported((int)d->bits, d->group)) return false;
-  return ctx->gemv_path == 2 || (ctx->gemv_path == 0 && m > 1);
+  return ctx->gemv_path == 2 || ((ctx->gemv_path == 0 || ctx->gemv_path == 3) && m > 1);
 }
 
 ztvm::GemvParams gemv_params(const ztvm_mm_desc* d, void* y, const void* x, const void* s, const void* w,
@@ -182,7 +185,7 @@ ztvm_status ztvm_init(int32_t device_ordinal, ztvm_ctx** out_ctx) {
   const char* mg = getenv("ZTVM_MOE_GROUPED");
   c->moe_grouped = !mg ? -1 : (mg[0] == '1' ? 1 : 0);
   const char* gp = getenv("ZTVM_GEMV_PATH");
-  c->gemv_path = !gp ? 0 : !strcmp(gp, "fma") ? 1 : !strcmp(gp, "mma") ? 2 : 0;
+  c->gemv_path = !gp ? 0 : !strcmp(gp, "fma") ? 1 : !strcmp(gp, "mma") ? 2 : !strcmp(gp, "tc_m2") ? 3 : 0;
   c->magic = kMagic;
   *out_ctx = c;
   return ZTVM_OK;
@@ -233,7 +236,9 @@ ztvm_status ztvm_int4_matmul(ztvm_ctx* ctx, const ztvm_mm_desc* d, void* y, cons
     p.X = static_cast<const __half*>(x) + (size_t)m0 * d->K;
     p.Y = d->out_f32 ? static_cast<void*>(static_cast<float*>(y) + (size_t)m0 * d->N)
                      : static_cast<void*>(static_cast<__half*>(y) + (size_t)m0 * d->N);
-    if (use_mma(ctx, d, dd.M)) ZTVM_CUDA(ztvm::launch_gemv_mma(p, false, 1, 1, st));
+    const bool want_tc = ctx->gemv_path == 0 || (ctx->gemv_path == 3 && dd.M > 1);
+    if (want_tc && ztvm::gemv_tc_supported(p, (int)d->bits, ctx->sm_count)) ZTVM_CUDA(ztvm::launch_gemv_tc(p, ctx->sm_count, st));
+    else if (use_mma(ctx, d, dd.M)) ZTVM_CUDA(ztvm::launch_gemv_mma(p, false, 1, 1, st));
     else ZTVM_CUDA(ztvm::launch_gemv(p, (int)d->bits, false, 1, 1, ctx->sm_count, st));
   }
   return ZTVM_OK;

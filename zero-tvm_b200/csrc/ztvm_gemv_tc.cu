@@ -1,0 +1,373 @@
+// Persistent decode GEMV for 4-bit / group-64 weights, M = 1..8, with the warp-level matrix unit as the multiplier
+// array (int4_matmul.gen.ts:170-571 for M = 1, :580-695 for the runtime-M matvec).
+//
+// Why this shape. At HBM rate one SM has to consume ~45 codes per clock. The CUDA-core paths top out near 54
+// (M = 1) and pay M times the FMAs for M > 1; mma.sync.m16n8k16 multiplies 16 weight rows x 16 codes x 8 tokens per
+// instruction (measured 73 codes/clk/SM with the unpack below), the same for every M <= 8. So the kernel is built
+// around keeping the memory pipe full and the per-tile fixed work small:
+//   * grid = one CTA per SM; CTA b owns the contiguous rows [b*N/G, (b+1)*N/G): perfectly balanced in bytes.
+//   * K is cut in slices of 256 codes. Warp (ks, rg) owns slice ks of the current K tile (16 slices = 4096 codes)
+//     and walks the CTA's 16-row tiles rg, rg+RG, ...; with K < 4096 the spare warps take other row tiles (RG > 1).
+//     The activations of a slice live in registers as ready-made B fragments (32 registers), loaded once per K
+//     tile: no shared-memory traffic for x at all.
+//   * weights, scales and biases of a (tile, slice) -- 16 x 128 B + 16 x 16 B -- travel global -> shared with
+//     per-lane cp.async into a ring of kTcDepth stages per warp (147 KB in flight per SM); no block-level barrier
+//     is involved in the streaming itself.
+//   * a nibble masked where it sits is an f16 subnormal (q * 2^-24 or q * 2^-20): the A fragments are 2 shifts and
+//     8 ANDs per 16 codes, the products are exact, each 64-code group is summed inside the matrix unit and folded
+//     into the f32 accumulators with round-to-nearest FMAs:  acc += s*2^24*lo + s*2^20*hi + b*sum(x).
+//   * every kTcRounds rounds the K-slice partials of the warps meet in shared memory (double-buffered, one
+//     __syncthreads per meeting, fixed summation order: results are deterministic).
+#include "ztvm_device.cuh"
+#include "ztvm_kernels.h"
+
+namespace ztvm {
+
+constexpr int kTcWarps = 16;
+constexpr int kTcDepth = 4;
+constexpr int kTcSlice = 256;                        // codes per warp slice = 128 B per row = 4 scale groups
+constexpr int kTcTileW = 16 * 128;                   // packed codes of one (tile, slice)
+constexpr int kTcTileBytes = kTcTileW + 16 * 16;     // + per row 4 scales, 4 biases (f16)
+constexpr int kTcRingBytes = kTcWarps * kTcDepth * kTcTileBytes;
+constexpr uint32_t kTcMaxAccBytes = 32 * 1024;       // cross-K-tile accumulators (only when K > 4096)
+
+__device__ __forceinline__ void tc_mma(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                       uint32_t b1, const float (&c)[4]) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
+}
+__device__ __forceinline__ void tc_cp16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void tc_cp8(uint32_t dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void tc_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ uint2 tc_lds64(uint32_t a) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint4 tc_lds128(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+  return v;
+}
+
+// rounds between two meetings: the partial buffers hold 2 x warps x rounds x 16 rows x NT floats
+__host__ __device__ constexpr int tc_rounds(int nt) { return nt <= 2 ? 4 : 2; }
+
+__device__ __forceinline__ uint32_t tc_lds32(uint32_t a) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint32_t tc_lds16(uint32_t a) {
+  unsigned short v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
+  return v;
+}
+
+// NT = tokens padded to a power of two. The eight columns of an MMA are (group, token) pairs: with NT tokens one
+// accumulator collects GPA = 8 / NT scale groups side by side (the B fragment of a column is zero in the MMAs of the
+// other groups), so the per-group fold after the MMAs is spread over the lanes of a quad instead of being repeated
+// by each of them: lane (g, c) owns columns 2c and 2c + 1.
+template <int NT, bool AFFINE>
+__global__ void __launch_bounds__(kTcWarps * 32, 1)
+gemv_tc_kernel(const GemvParams p) {
+  extern __shared__ __align__(128) uint8_t tc_smem[];
+  constexpr int GPA = 8 / NT;                               // groups per accumulator (only 4 exist per tile)
+  constexpr int NA = GPA >= 4 ? 1 : 4 / GPA;                // accumulators per tile
+  constexpr int kTcRounds = tc_rounds(NT);                  // rounds between two meetings of the K-slice partials
+  constexpr int kBlkRows = kTcRounds * 16;                  // rows a warp covers between two meetings
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, c = lane & 3;
+
+  const uint32_t slices = p.K / kTcSlice;
+  const uint32_t KS = slices < (uint32_t)kTcWarps ? slices : (uint32_t)kTcWarps;
+  const uint32_t RG = (uint32_t)kTcWarps / KS;
+  const uint32_t ks = (uint32_t)warp % KS, rg = (uint32_t)warp / KS;
+  const bool warp_active = rg < RG;
+  const uint32_t num_kt = (slices + KS - 1) / KS;
+
+  const uint32_t r0 = (uint32_t)((uint64_t)blockIdx.x * p.N / gridDim.x);
+  const uint32_t r1 = (uint32_t)((uint64_t)(blockIdx.x + 1) * p.N / gridDim.x);
+  const uint32_t nrows = r1 - r0;
+  const uint32_t ntiles = (nrows + 15) / 16;
+  uint32_t rounds = (ntiles + RG - 1) / RG;
+  rounds = (rounds + kTcRounds - 1) / kTcRounds * kTcRounds;
+  const uint32_t total = num_kt * rounds;                   // (K tile, round) steps of every warp
+
+  const uint32_t ring = (uint32_t)__cvta_generic_to_shared(tc_smem) + (uint32_t)warp * (kTcDepth * kTcTileBytes);
+  float* partial = reinterpret_cast<float*>(tc_smem + kTcRingBytes);            // [2][warps][kBlkRows][NT]
+  float* acc_sm = partial + 2 * kTcWarps * kBlkRows * NT;                       // [nrows][M], only if num_kt > 1
+
+  // ---- producer side: one (tile, slice) per step, issued kTcDepth - 1 steps ahead ----------------------------
+  const uint32_t cp_row = (uint32_t)lane >> 3, cp_chunk = (uint32_t)lane & 7;   // codes: 4 rows x 8 chunks per pass
+  const uint32_t sb_row = (uint32_t)lane >> 1, sb_which = (uint32_t)lane & 1;   // scales / biases: 16 rows x 2
+  const uint32_t cp_dst = cp_row * 128 + (((cp_chunk >> 1) ^ (cp_row & 3)) << 5) + ((cp_chunk & 1) << 4);
+  const uint32_t sb_dst = kTcTileW + sb_row * 16 + sb_which * 8;
+  const size_t row4 = (size_t)4 * p.KP;
+  uint32_t i_step = 0, i_kt = 0, i_rd = 0;                  // the next step to issue, as (K tile, round)
+  auto issue = [&]() {
+    if (warp_active && i_step < total) {
+      const uint32_t sl = i_kt * KS + ks;
+      const uint32_t trow = (i_rd * RG + rg) * 16;          // first row of the tile, CTA-relative
+      if (sl < slices && trow < nrows) {
+        const uint32_t st = ring + (i_step % kTcDepth) * kTcTileBytes;
+        const uint32_t* src = p.W + (size_t)(r0 + trow + cp_row) * p.KP + sl * 32 + cp_chunk * 4;
+        const __half* sbp = (sb_which ? p.B : p.S) + (size_t)(r0 + trow + sb_row) * p.SPR + sl * 4;
+        if (trow + 16 <= nrows) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) tc_cp16(st + cp_dst + i * 512, src + i * row4);   // (row + 4i) & 3 == row & 3
+          if (AFFINE || sb_which == 0) tc_cp8(st + sb_dst, sbp);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            if (trow + cp_row + 4 * i < nrows) tc_cp16(st + cp_dst + i * 512, src + i * row4);
+          if (trow + sb_row < nrows && (AFFINE || sb_which == 0)) tc_cp8(st + sb_dst, sbp);
+        }
+      }
+    }
+    tc_commit();
+    ++i_step;
+    if (++i_rd == rounds) { i_rd = 0; ++i_kt; }
+  };
+#pragma unroll
+  for (int i = 0; i < kTcDepth - 1; ++i) issue();
+
+  // everything above reads only weights; activations and outputs belong to the stream order
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  // B fragments of this warp's slice: column g of the MMA = (group jn within an accumulator, token tn)
+  uint32_t xf[4][2][4];          // [group][word step][lo k0-7, lo k8-15, hi k0-7, hi k8-15]
+  float xs[NA][2];               // sum of x over the group that column 2c + v of accumulator a stands for
+  const int jn = g / NT, tn = g % NT;
+  auto load_x = [&](uint32_t kt) {
+    const uint32_t sl = kt * KS + ks;
+    const bool tok_ok = warp_active && sl < slices && (uint32_t)tn < p.M;
+    const __half* xr = p.X + (size_t)tn * p.x_row_stride + (size_t)sl * kTcSlice;
+    float part[4];
+#pragma unroll
+    for (int tq = 0; tq < 4; ++tq) {
+      const bool on = tok_ok && (tq % GPA) == jn;
+      float sum = 0.f;
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+        if (on) raw = *reinterpret_cast<const uint4*>(xr + (8 * tq + 2 * c + u) * 8);
+        // raw = (x0x1, x2x3, x4x5, x6x7) -> (x0x4, x2x6 | x1x5, x3x7): the pair order of the masked code words
+        xf[tq][u][0] = __byte_perm(raw.x, raw.z, 0x5410);
+        xf[tq][u][1] = __byte_perm(raw.y, raw.w, 0x5410);
+        xf[tq][u][2] = __byte_perm(raw.x, raw.z, 0x7632);
+        xf[tq][u][3] = __byte_perm(raw.y, raw.w, 0x7632);
+        const float2 a = __half22float2(u32_as_h2(raw.x)), b = __half22float2(u32_as_h2(raw.y)),
+                     d = __half22float2(u32_as_h2(raw.z)), e = __half22float2(u32_as_h2(raw.w));
+        sum += ((a.x + a.y) + (b.x + b.y)) + ((d.x + d.y) + (e.x + e.y));
+      }
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);          // every lane of quad g: sum over group tq of token tn
+      part[tq] = sum;
+    }
+#pragma unroll
+    for (int a = 0; a < NA; ++a)
+#pragma unroll
+      for (int v = 0; v < 2; ++v) {
+        const int col = 2 * c + v, want = a * GPA + col / NT;   // the group this lane folds for that column
+        float r = 0.f;
+#pragma unroll
+        for (int tq = 0; tq < 4; ++tq) {
+          const float t = __shfl_sync(0xffffffffu, part[tq], col * 4);
+          if (tq == want) r = t;
+        }
+        xs[a][v] = r;
+      }
+  };
+  load_x(0);
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+  float acc[kTcRounds][2][2];
+#pragma unroll
+  for (int q = 0; q < kTcRounds; ++q)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) acc[q][h][0] = acc[q][h][1] = 0.f;
+  const float kZero[4] = {0.f, 0.f, 0.f, 0.f};
+  const uint32_t swz = ((uint32_t)g & 3u);
+  // where this lane finds the scale (and, 8 bytes on, the bias) of the group it folds, inside a row's 16 bytes
+  const uint32_t sc_off = NT == 1 ? 4u * ((uint32_t)c & 1u) : NT == 2 ? 2u * (uint32_t)c : NT == 4 ? 2u * ((uint32_t)c >> 1) : 0u;
+
+  uint32_t step = 0, meet = 0;   // meet: running count of meetings, its parity picks the partial buffer
+  for (uint32_t kt = 0; kt < num_kt; ++kt) {
+    if (kt) load_x(kt);
+    const bool slice_ok = warp_active && kt * KS + ks < slices;
+    for (uint32_t blk = 0; blk < rounds / kTcRounds; ++blk, ++meet) {
+#pragma unroll
+      for (int q = 0; q < kTcRounds; ++q, ++step) {
+        issue();
+        asm volatile("cp.async.wait_group %0;" ::"n"(kTcDepth - 1) : "memory");
+        __syncwarp();
+        const uint32_t trow = ((blk * kTcRounds + q) * RG + rg) * 16;
+        if (slice_ok && trow < nrows) {
+          const uint32_t st = ring + (step % kTcDepth) * kTcTileBytes;
+          float clo[NA][4], chi[NA][4];
+#pragma unroll
+          for (int tq = 0; tq < 4; ++tq) {
+            const int a = NA == 1 ? 0 : tq / GPA;
+            const bool first = NA == 1 ? tq == 0 : (tq % GPA) == 0;
+            const uint32_t off = (((uint32_t)tq ^ swz) << 5) + ((uint32_t)c << 3);
+            const uint2 wg = tc_lds64(st + (uint32_t)g * 128 + off), wh = tc_lds64(st + (uint32_t)(g + 8) * 128 + off);
+            {
+              const uint32_t ug = wg.x >> 8, uh = wh.x >> 8;
+              if (first) {
+                tc_mma(clo[a], wg.x & 0x000F000Fu, wh.x & 0x000F000Fu, ug & 0x000F000Fu, uh & 0x000F000Fu, xf[tq][0][0], xf[tq][0][1], kZero);
+                tc_mma(chi[a], wg.x & 0x00F000F0u, wh.x & 0x00F000F0u, ug & 0x00F000F0u, uh & 0x00F000F0u, xf[tq][0][2], xf[tq][0][3], kZero);
+              } else {
+                tc_mma(clo[a], wg.x & 0x000F000Fu, wh.x & 0x000F000Fu, ug & 0x000F000Fu, uh & 0x000F000Fu, xf[tq][0][0], xf[tq][0][1], clo[a]);
+                tc_mma(chi[a], wg.x & 0x00F000F0u, wh.x & 0x00F000F0u, ug & 0x00F000F0u, uh & 0x00F000F0u, xf[tq][0][2], xf[tq][0][3], chi[a]);
+              }
+            }
+            {
+              const uint32_t ug = wg.y >> 8, uh = wh.y >> 8;
+              tc_mma(clo[a], wg.y & 0x000F000Fu, wh.y & 0x000F000Fu, ug & 0x000F000Fu, uh & 0x000F000Fu, xf[tq][1][0], xf[tq][1][1], clo[a]);
+              tc_mma(chi[a], wg.y & 0x00F000F0u, wh.y & 0x00F000F0u, ug & 0x00F000F0u, uh & 0x00F000F0u, xf[tq][1][2], xf[tq][1][3], chi[a]);
+            }
+          }
+          // fold: column 2c + v of accumulator a is one (group, token); its scale and bias sit at sc_off (+ 8)
+#pragma unroll
+          for (int a = 0; a < NA; ++a)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const uint32_t rowp = st + kTcTileW + (uint32_t)(g + 8 * h) * 16 + sc_off + (NT == 4 ? 4u * a : NT == 8 ? 2u * a : 0u);
+              float s[2], b[2];
+              if constexpr (NT == 1) {      // columns 2c, 2c + 1 are two groups
+                const float2 s2 = __half22float2(u32_as_h2(tc_lds32(rowp)));
+                s[0] = s2.x; s[1] = s2.y;
+                if (AFFINE) {
+                  const float2 b2 = __half22float2(u32_as_h2(tc_lds32(rowp + 8)));
+                  b[0] = b2.x; b[1] = b2.y;
+                }
+              } else {                      // both columns belong to one group
+                s[0] = s[1] = __half2float(__ushort_as_half((unsigned short)tc_lds16(rowp)));
+                if (AFFINE) b[0] = b[1] = __half2float(__ushort_as_half((unsigned short)tc_lds16(rowp + 8)));
+              }
+              if (!AFFINE) { b[0] = -7.f * s[0]; b[1] = -7.f * s[1]; }
+#pragma unroll
+              for (int v = 0; v < 2; ++v) {
+                const float t = fmaf(clo[a][2 * h + v], 16.f, chi[a][2 * h + v]);   // (2^24 lo + 2^20 hi) / 2^20
+                float r = acc[q][h][v];
+                r = fmaf(s[v] * 1048576.f, t, r);
+                r = fmaf(b[v], xs[a][v], r);
+                acc[q][h][v] = r;
+              }
+            }
+        }
+        __syncwarp();   // every lane is done with the stage before the next issue refills it
+      }
+      // ---- meeting: K-slice partials of the block's rows -> shared, then one fixed-order sum per output --------
+      float* mine = partial + ((size_t)((meet & 1u) * kTcWarps + (uint32_t)warp) * kBlkRows) * NT;
+#pragma unroll
+      for (int q = 0; q < kTcRounds; ++q)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          float v0 = slice_ok ? acc[q][h][0] : 0.f, v1 = slice_ok ? acc[q][h][1] : 0.f;
+          acc[q][h][0] = acc[q][h][1] = 0.f;
+          float* dst = mine + (q * 16 + g + 8 * h) * NT;
+          if constexpr (NT == 1) {          // the quad's columns are groups of token 0
+            v0 += v1;
+            v0 += __shfl_xor_sync(0xffffffffu, v0, 1);
+            if (c == 0) dst[0] = v0;
+          } else if constexpr (NT == 2) {   // lane c holds group c of tokens 0, 1
+            v0 += __shfl_xor_sync(0xffffffffu, v0, 1); v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
+            v0 += __shfl_xor_sync(0xffffffffu, v0, 2); v1 += __shfl_xor_sync(0xffffffffu, v1, 2);
+            if (c == 0) *reinterpret_cast<float2*>(dst) = make_float2(v0, v1);
+          } else if constexpr (NT == 4) {   // lanes c and c ^ 2 hold the two groups of tokens 2(c & 1) + v
+            v0 += __shfl_xor_sync(0xffffffffu, v0, 2); v1 += __shfl_xor_sync(0xffffffffu, v1, 2);
+            if (c < 2) *reinterpret_cast<float2*>(dst + 2 * c) = make_float2(v0, v1);
+          } else {
+            *reinterpret_cast<float2*>(dst + 2 * c) = make_float2(v0, v1);
+          }
+        }
+      __syncthreads();
+      const float* buf = partial + (size_t)(meet & 1u) * kTcWarps * kBlkRows * NT;
+      const uint32_t outs = (uint32_t)kTcRounds * RG * 16u * p.M;
+      // the meeting's sums are taken by a different warp each time, so no warp falls behind the others for good
+      for (uint32_t i = (threadIdx.x + 512u - 32u * (meet & 15u)) & 511u; i < outs; i += blockDim.x) {
+        const uint32_t tok = i % p.M, br = i / p.M;           // br: row inside the block's R*RG tiles
+        const uint32_t r16 = br & 15u, tb = br >> 4;
+        const uint32_t q = tb / RG, rgi = tb - q * RG;
+        const uint32_t row = ((blk * kTcRounds + q) * RG + rgi) * 16 + r16;
+        if (row >= nrows) continue;
+        float v = 0.f;
+        for (uint32_t k2 = 0; k2 < KS; ++k2) v += buf[((size_t)(rgi * KS + k2) * kBlkRows + q * 16 + r16) * NT + tok];
+        if (num_kt > 1) {
+          float* a = acc_sm + (size_t)row * p.M + tok;
+          if (kt) v += *a;
+          if (kt + 1 < num_kt) { *a = v; continue; }
+        }
+        const size_t o = (size_t)tok * p.y_row_stride + r0 + row;
+        if (p.out_f32) reinterpret_cast<float*>(p.Y)[o] = v;
+        else reinterpret_cast<__half*>(p.Y)[o] = __float2half_rn(v);
+      }
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+
+// ---- host side --------------------------------------------------------------------------------------------
+bool gemv_tc_supported(const GemvParams& p, int bits, int sm_count) {
+  if (bits != 4 || p.group_shift != 6 || p.M < 1 || p.M > 8) return false;
+  if (p.K % kTcSlice || p.K == 0 || p.N == 0) return false;
+  if (p.x_row_stride % 8 || (reinterpret_cast<uintptr_t>(p.X) & 15u)) return false;
+  if ((reinterpret_cast<uintptr_t>(p.W) & 15u) || (reinterpret_cast<uintptr_t>(p.S) & 7u) ||
+      (p.B && (reinterpret_cast<uintptr_t>(p.B) & 7u)))
+    return false;
+  const uint32_t slices = p.K / kTcSlice;
+  if (slices > (uint32_t)kTcWarps) {   // several K tiles: the running sums of the CTA's rows sit in shared memory
+    const uint32_t grid = p.N < (uint32_t)sm_count ? p.N : (uint32_t)sm_count;
+    const uint64_t rows = ((uint64_t)p.N + grid - 1) / grid + 1;
+    if (rows * p.M * 4 > kTcMaxAccBytes) return false;
+  }
+  return true;
+}
+
+template <int NT, bool AFFINE>
+static cudaError_t launch_tc_one(const GemvParams& p, unsigned grid, size_t smem, cudaStream_t st) {
+  auto kern = gemv_tc_kernel<NT, AFFINE>;
+  static bool attr_set[16] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 16 && !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return e;
+    attr_set[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kTcWarps * 32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, p);
+}
+
+cudaError_t launch_gemv_tc(const GemvParams& p, int sm_count, cudaStream_t st) {
+  const unsigned grid = p.N < (uint32_t)sm_count ? p.N : (unsigned)sm_count;
+  const int nt = p.M == 1 ? 1 : p.M == 2 ? 2 : p.M <= 4 ? 4 : 8;
+  size_t smem = kTcRingBytes + (size_t)2 * kTcWarps * tc_rounds(nt) * 16 * nt * 4;
+  if (p.K / kTcSlice > (uint32_t)kTcWarps) smem += (((size_t)p.N + grid - 1) / grid + 1) * p.M * 4;
+  const bool affine = p.B != nullptr;
+  switch (nt) {
+    case 1: return affine ? launch_tc_one<1, true>(p, grid, smem, st) : launch_tc_one<1, false>(p, grid, smem, st);
+    case 2: return affine ? launch_tc_one<2, true>(p, grid, smem, st) : launch_tc_one<2, false>(p, grid, smem, st);
+    case 4: return affine ? launch_tc_one<4, true>(p, grid, smem, st) : launch_tc_one<4, false>(p, grid, smem, st);
+    default: return affine ? launch_tc_one<8, true>(p, grid, smem, st) : launch_tc_one<8, false>(p, grid, smem, st);
+  }
+}
+
+}  // namespace ztvm
