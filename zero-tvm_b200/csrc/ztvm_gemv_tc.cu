@@ -56,6 +56,23 @@ __device__ __forceinline__ uint4 tc_lds128(uint32_t a) {
   return v;
 }
 
+// packed f32 pairs: sm_100 has a two-wide f32 FMA (fma.rn.f32x2), which halves the instructions of the group fold
+__device__ __forceinline__ unsigned long long tc_pk(float a, float b) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ float2 tc_unpk(unsigned long long v) {
+  float2 r;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(r.x), "=f"(r.y) : "l"(v));
+  return r;
+}
+__device__ __forceinline__ unsigned long long tc_ffma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+  unsigned long long d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+
 // rounds between two meetings: the partial buffers hold 2 x warps x rounds x 16 rows x NT floats
 __host__ __device__ constexpr int tc_rounds(int nt) { return nt <= 2 ? 4 : 2; }
 
@@ -143,7 +160,7 @@ gemv_tc_kernel(const GemvParams p) {
 
   // B fragments of this warp's slice: column g of the MMA = (group jn within an accumulator, token tn)
   uint32_t xf[4][2][4];          // [group][word step][lo k0-7, lo k8-15, hi k0-7, hi k8-15]
-  float xs[NA][2];               // sum of x over the group that column 2c + v of accumulator a stands for
+  unsigned long long xs2[NA];    // sums of x over the groups that columns 2c, 2c + 1 of accumulator a stand for
   const int jn = g / NT, tn = g % NT;
   auto load_x = [&](uint32_t kt) {
     const uint32_t sl = kt * KS + ks;
@@ -172,7 +189,8 @@ gemv_tc_kernel(const GemvParams p) {
       part[tq] = sum;
     }
 #pragma unroll
-    for (int a = 0; a < NA; ++a)
+    for (int a = 0; a < NA; ++a) {
+      float r2[2];
 #pragma unroll
       for (int v = 0; v < 2; ++v) {
         const int col = 2 * c + v, want = a * GPA + col / NT;   // the group this lane folds for that column
@@ -182,17 +200,18 @@ gemv_tc_kernel(const GemvParams p) {
           const float t = __shfl_sync(0xffffffffu, part[tq], col * 4);
           if (tq == want) r = t;
         }
-        xs[a][v] = r;
+        r2[v] = r;
       }
+      xs2[a] = tc_pk(r2[0], r2[1]);
+    }
   };
   load_x(0);
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-  float acc[kTcRounds][2][2];
+  unsigned long long acc[kTcRounds][2];   // per round and row half: the two columns of this lane, packed
 #pragma unroll
-  for (int q = 0; q < kTcRounds; ++q)
-#pragma unroll
-    for (int h = 0; h < 2; ++h) acc[q][h][0] = acc[q][h][1] = 0.f;
+  for (int q = 0; q < kTcRounds; ++q) acc[q][0] = acc[q][1] = 0ull;
+  const unsigned long long k16 = tc_pk(16.f, 16.f);
   const float kZero[4] = {0.f, 0.f, 0.f, 0.f};
   const uint32_t swz = ((uint32_t)g & 3u);
   // where this lane finds the scale (and, 8 bytes on, the bias) of the group it folds, inside a row's 16 bytes
@@ -253,14 +272,12 @@ gemv_tc_kernel(const GemvParams p) {
                 if (AFFINE) b[0] = b[1] = __half2float(__ushort_as_half((unsigned short)tc_lds16(rowp + 8)));
               }
               if (!AFFINE) { b[0] = -7.f * s[0]; b[1] = -7.f * s[1]; }
-#pragma unroll
-              for (int v = 0; v < 2; ++v) {
-                const float t = fmaf(clo[a][2 * h + v], 16.f, chi[a][2 * h + v]);   // (2^24 lo + 2^20 hi) / 2^20
-                float r = acc[q][h][v];
-                r = fmaf(s[v] * 1048576.f, t, r);
-                r = fmaf(b[v], xs[a][v], r);
-                acc[q][h][v] = r;
-              }
+              // (2^24 lo + 2^20 hi) / 2^20, then the scale and the bias term, two columns per instruction
+              const unsigned long long t2 = tc_ffma2(tc_pk(clo[a][2 * h], clo[a][2 * h + 1]), k16, tc_pk(chi[a][2 * h], chi[a][2 * h + 1]));
+              unsigned long long r = acc[q][h];
+              r = tc_ffma2(tc_pk(s[0] * 1048576.f, s[1] * 1048576.f), t2, r);
+              r = tc_ffma2(tc_pk(b[0], b[1]), xs2[a], r);
+              acc[q][h] = r;
             }
         }
         __syncwarp();   // every lane is done with the stage before the next issue refills it
@@ -271,8 +288,9 @@ gemv_tc_kernel(const GemvParams p) {
       for (int q = 0; q < kTcRounds; ++q)
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          float v0 = slice_ok ? acc[q][h][0] : 0.f, v1 = slice_ok ? acc[q][h][1] : 0.f;
-          acc[q][h][0] = acc[q][h][1] = 0.f;
+          const float2 av = tc_unpk(acc[q][h]);
+          float v0 = slice_ok ? av.x : 0.f, v1 = slice_ok ? av.y : 0.f;
+          acc[q][h] = 0ull;
           float* dst = mine + (q * 16 + g + 8 * h) * NT;
           if constexpr (NT == 1) {          // the quad's columns are groups of token 0
             v0 += v1;
