@@ -127,10 +127,12 @@ ZTVM_API ztvm_status ztvm_int4_matmul_moe(ztvm_ctx* ctx, const ztvm_moe_desc* de
  * buffer that grows on demand; this entry point keeps it in a fixed array inside the library's device image
  * and makes no allocating call at all.
  *  - Limits: tokens*slots <= ZTVM_MOE_NOALLOC_MAX_PAIRS and experts <= ZTVM_MOE_NOALLOC_MAX_EXPERTS, else
- *    ZTVM_ERR_TOO_LARGE. Only the tensor-core form runs here: bits 4, group 64, K % 64 == 0, N % 128 == 0,
- *    strides multiples of 8 elements, y 16-byte aligned; anything else is ZTVM_ERR_UNSUPPORTED /
- *    ZTVM_ERR_ALIGNMENT (there is no fall-back to the per-pair kernel). Results are those of
- *    ztvm_int4_matmul_moe on the same inputs, bit for bit.
+ *    ZTVM_ERR_TOO_LARGE. Only the two grouped kernels run here (there is no fall-back to the per-pair kernel):
+ *    bits 4, group 64, and either K % 256 == 0, K <= 4096, N % 16 == 0 (streaming kernel) or K % 64 == 0,
+ *    N % 128 == 0, output strides multiples of 8 elements, y 16-byte aligned (tensor-core tiles); input strides
+ *    multiples of 8 elements. Anything else is ZTVM_ERR_UNSUPPORTED / ZTVM_ERR_ALIGNMENT. The kernel is chosen
+ *    exactly as ztvm_int4_matmul_moe chooses it, so the results are those of that call on the same inputs, bit
+ *    for bit.
  *  - The first call on a device looks up the array's device address and loads the kernels: make one call
  *    per device at start-up, before any stream capture.
  *  - There is ONE array per device, shared by every context and stream: two calls that overlap in time on

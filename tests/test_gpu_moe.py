@@ -11,6 +11,17 @@ pytestmark = pytest.mark.gpu
 TOL = 2e-3   # with the scale-tied floor of oracle.rel_err_scaled (1e-3 of the output rms)
 
 
+def moe_kernel_kind(pairs, experts, K, N, bits):
+    """Which kernel ztvm_int4_matmul_moe picks (mirrors moe_pick in ztvm_api.cu): 'pair', 'stream' or 'tiles'."""
+    if bits != 4 or pairs < 128 or experts > 1024:
+        return "pair"
+    tiles_ok = K % 64 == 0 and N % 128 == 0
+    stream_ok = K % 256 == 0 and K <= 4096 and N % 16 == 0
+    if stream_ok and (pairs < 24 * experts or not tiles_ok):
+        return "stream"
+    return "tiles" if tiles_ok else "pair"
+
+
 def run_block(backend, dev, mb, K_top=8, bits=4):
     """router -> gate, up -> silu -> down -> combine with the engine's buffers and PODArgs."""
     T, E, d, ffn = mb["T"], mb["E"], mb["hidden"], mb["ffn"]
@@ -41,24 +52,29 @@ def run_block(backend, dev, mb, K_top=8, bits=4):
                 y_slots=dev.get(y_slots), y=dev.get(y))
 
 
-def check_block(got, mb, oracle_c, K_top=8, bits=4):
+def check_block(got, mb, oracle_c, K_top=8, bits=4, pairs_run=None):
+    """pairs_run: (token, slot) pairs of the launch that produced `got`, when `mb` is only a sample of its tokens."""
     T, E, d, ffn = mb["T"], mb["E"], mb["hidden"], mb["ffn"]
     ids_ref, sc_ref = oracle_c.router_topk(mb["logits"], E, K_top, True, mb["has_shared"])
     # routing: indices exact, scores 2e-6 (tests/kernels/run.mjs:333-336)
     assert np.array_equal(got["ids"], ids_ref)
     assert np.abs(got["scores"] - sc_ref).max() < 2e-6
-    # each stage against the f64 anchor computed from the GPU's own (already checked) inputs. From 128 (token, slot)
-    # pairs on, 4-bit experts run as a grouped tensor-core GEMM: f16 weights (anchor over W16) and the GEMM floor.
-    grouped = bits == 4 and ids_ref.size >= 128 and ffn % 128 == 0 and d % 128 == 0
-    frac = 1e-2 if grouped else 1e-3
-    g64 = oracle_c.moe_matmul_f64(mb["x"], *mb["gate"], ids_ref, ffn, d, 64, bits, in_per_slot=False, w16=grouped)
-    u64 = oracle_c.moe_matmul_f64(mb["x"], *mb["up"], ids_ref, ffn, d, 64, bits, in_per_slot=False, w16=grouped)
-    assert zo.rel_err_scaled(got["gate_up"][..., :ffn], g64, frac) <= TOL
-    assert zo.rel_err_scaled(got["gate_up"][..., ffn:], u64, frac) <= TOL
+    # each stage against the f64 anchor computed from the GPU's own (already checked) inputs. The anchor follows the
+    # kernel that ran: the tensor-core tiles multiply f16 weights (anchor over W16, GEMM floor), the per-pair GEMV and
+    # the streaming grouped kernel multiply the codes exactly (anchor over fl32(s*q+b), GEMV floor).
+    experts = E + int(mb["has_shared"])
+    def anchor(x_in, proj, N, K, per_slot):
+        tiles = moe_kernel_kind(pairs_run or ids_ref.size, experts, K, N, bits) == "tiles"
+        ref = oracle_c.moe_matmul_f64(x_in, *mb[proj], ids_ref, N, K, 64, bits, in_per_slot=per_slot, w16=tiles)
+        return ref, (1e-2 if tiles else 1e-3)
+    g64, fr = anchor(mb["x"], "gate", ffn, d, False)
+    assert zo.rel_err_scaled(got["gate_up"][..., :ffn], g64, fr) <= TOL
+    u64, fr = anchor(mb["x"], "up", ffn, d, False)
+    assert zo.rel_err_scaled(got["gate_up"][..., ffn:], u64, fr) <= TOL
     h_ref = oracle_c.silu_mul(got["gate_up"], ffn)
     assert zo.rel_err_scaled(got["h"], h_ref.astype(np.float64)) <= TOL
-    d64 = oracle_c.moe_matmul_f64(got["h"], *mb["down"], ids_ref, d, ffn, 64, bits, in_per_slot=True, w16=grouped)
-    assert zo.rel_err_scaled(got["y_slots"], d64, frac) <= TOL
+    d64, fr = anchor(got["h"], "down", d, ffn, True)
+    assert zo.rel_err_scaled(got["y_slots"], d64, fr) <= TOL
     y_ref = oracle_c.moe_combine(got["y_slots"], got["scores"])
     assert np.array_equal(got["y"].view(np.uint16), y_ref.view(np.uint16))
     assert np.isfinite(got["y"].astype(np.float32)).all()
@@ -124,7 +140,7 @@ def test_full_size_block_properties(backend, dev, oracle_c):
     sel = np.random.default_rng(1).choice(T, 24, replace=False)
     sub = dict(mb, T=len(sel), x=mb["x"][sel], logits=mb["logits"][sel])
     sub_got = {k: v[sel] for k, v in got.items()}
-    check_block(sub_got, sub, oracle_c)
+    check_block(sub_got, sub, oracle_c, pairs_run=ids_ref.size)
     perm = np.random.default_rng(2).permutation(T)
     got_p = run_block(backend, dev, dict(mb, x=mb["x"][perm], logits=mb["logits"][perm]))
     assert np.array_equal(got_p["y"].view(np.uint16), got["y"][perm].view(np.uint16))
@@ -163,9 +179,34 @@ def test_grouped_path_handles_bad_ids_and_matches_per_pair_path(backend, dev, or
     got = dev.get(out)
     assert (got[3, 2, :128] == 7.0).all() and (got[..., 128:] == 7.0).all()
     ids_ok = ids.copy(); ids_ok[3, 2] = 0
-    ref = oracle_c.moe_matmul_f64(mb["x"], *mb["gate"], ids_ok, 128, 256, 64, 4, in_per_slot=False, w16=True)
+    tiles = moe_kernel_kind(ids.size, 9, 256, 128, 4) == "tiles"
+    ref = oracle_c.moe_matmul_f64(mb["x"], *mb["gate"], ids_ok, 128, 256, 64, 4, in_per_slot=False, w16=tiles)
     mask = np.ones((32, slots), bool); mask[3, 2] = False
-    assert zo.rel_err_scaled(got[..., :128][mask], ref[mask], 1e-2) <= TOL
+    assert zo.rel_err_scaled(got[..., :128][mask], ref[mask], 1e-2 if tiles else 1e-3) <= TOL
+
+
+@pytest.mark.parametrize("forced,kind", [("2", "stream"), ("1", "tiles")])
+def test_forced_grouped_kernels_on_uneven_expert_loads(forced, kind, dev, oracle_c, monkeypatch):
+    """Either grouped kernel on a skewed routing: one expert takes a third of 300 pairs (many 8-pair chunks for the
+    streaming kernel, a full and a ragged 128-pair tile for the tensor-core one), some experts take none."""
+    monkeypatch.setenv("ZTVM_MOE_GROUPED", forced)
+    be = z.backend.CudaMatmulBackend(0)
+    mb = z.synth.moe_block(100, E=12, hidden=512, ffn=256, seed=21)
+    slots = 3
+    rng = np.random.default_rng(9)
+    ids = rng.choice(np.array([0, 2, 3, 5, 7, 11, 12], dtype=np.uint32), size=(100, slots)).astype(np.uint32)
+    ids[rng.random((100, slots)) < 0.34] = 5
+    out = dev.empty((100, slots, 2 * 256), np.float16, fill=7.0)
+    gw, gs, gb = (dev.put(a) for a in mb["gate"])
+    be.dispatch("int4_matmul_tiled_vec4h_affine_moe",
+                [out, dev.put(mb["x"]), gs, gw, moe_gate_pod_args(512, 256, slots), gb, dev.put(ids)], (64, 100, slots))
+    assert be.ctx.device_errors() == 0
+    got = dev.get(out)
+    assert (got[..., 256:] == 7.0).all()
+    got = got[..., :256]
+    tiles = kind == "tiles"
+    ref = oracle_c.moe_matmul_f64(mb["x"], *mb["gate"], ids, 256, 512, 64, 4, in_per_slot=False, w16=tiles)
+    assert zo.rel_err_scaled(got, ref, 1e-2 if tiles else 1e-3) <= TOL
 
 
 def test_moe_argument_errors(backend, dev):

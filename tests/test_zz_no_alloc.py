@@ -1,7 +1,7 @@
 """ztvm_int4_matmul_moe_noalloc: the grouped MoE matmul with its plan in a fixed device array.
 
-Checked through the C ABI against ztvm_int4_matmul_moe on the same inputs (which runs the same tensor-core tiles
-from 128 pairs on): bit-identical outputs, on two calls in a row, and again after the shapes changed in between.
+Checked through the C ABI against ztvm_int4_matmul_moe on the same inputs (from 128 pairs on both entry points pick
+the same grouped kernel; the cases below cover the streaming kernel and the tensor-core tiles): bit-identical outputs, on two calls in a row, and again after the shapes changed in between.
 The file name keeps it last in collection order, so it also runs after every other GPU test has used the library.
 """
 import numpy as np
@@ -48,6 +48,11 @@ def test_noalloc_matches_the_allocating_entry_twice_in_a_row(backend, dev):
     assert np.array_equal(ref2, new2)
     ref, new = both_entries(backend, dev, mb, ids, slots, seed_fill=9.0)
     assert np.array_equal(ref, new)
+    # many pairs per expert: both entry points run the tensor-core tiles
+    mb3 = z.synth.moe_block(192, E=2, hidden=256, ffn=128, seed=13)
+    ids3 = np.random.default_rng(5).integers(0, 3, size=(192, 3), dtype=np.uint32)
+    ref3, new3 = both_entries(backend, dev, mb3, ids3, 3, seed_fill=2.0)
+    assert np.array_equal(ref3, new3)
 
 
 def test_noalloc_counts_bad_ids_and_leaves_their_rows_alone(backend, dev):
@@ -81,8 +86,8 @@ def test_noalloc_refuses_what_does_not_fit_or_is_not_a_tile_shape(backend, dev):
     # refusals happen before any launch, so the (too small) buffers above are never touched
     for kw, code, word in ((dict(tokens=65536 // 3 + 1), z.capi.ERR_TOO_LARGE, "65536"),
                            (dict(experts=1025), z.capi.ERR_TOO_LARGE, "1024"),
-                           (dict(N=64), z.capi.ERR_UNSUPPORTED, "N"),
-                           (dict(out_tok=380), z.capi.ERR_ALIGNMENT, "strides")):
+                           (dict(N=72), z.capi.ERR_UNSUPPORTED, "N"),
+                           (dict(in_tok=252), z.capi.ERR_ALIGNMENT, "strides")):
         with pytest.raises(z.ZtvmError) as e:
             call(**kw)
         assert e.value.status == code and word in str(e.value), (kw, e.value)

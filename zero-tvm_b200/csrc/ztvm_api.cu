@@ -27,7 +27,9 @@ struct ztvm_ctx {
   // plan scratch of the grouped MoE matmul (grown on demand: a call that needs more synchronises the device,
   // reallocates and goes on; make one call at the largest size before capturing a graph)
   void* d_ws; size_t d_ws_bytes;
-  int moe_grouped;  // env ZTVM_MOE_GROUPED=0|1 forces the per-pair GEMV / the grouped GEMM (a measurement knob)
+  // env ZTVM_MOE_GROUPED (a measurement knob): 0 forces the per-pair GEMV, 1 the tensor-core tiles, 2 the streaming
+  // grouped kernel; unset = by size (below 128 pairs per-pair; then streaming while an expert sees few pairs)
+  int moe_grouped;
 };
 
 namespace {
@@ -183,7 +185,7 @@ ztvm_status ztvm_init(int32_t device_ordinal, ztvm_ctx** out_ctx) {
   const char* ng = getenv("ZTVM_NO_GEMM");
   c->no_gemm = (ng && ng[0] == '1') ? 1 : 0;
   const char* mg = getenv("ZTVM_MOE_GROUPED");
-  c->moe_grouped = !mg ? -1 : (mg[0] == '1' ? 1 : 0);
+  c->moe_grouped = !mg ? -1 : (mg[0] == '1' ? 1 : mg[0] == '2' ? 2 : 0);
   const char* gp = getenv("ZTVM_GEMV_PATH");
   c->gemv_path = !gp ? 0 : !strcmp(gp, "fma") ? 1 : !strcmp(gp, "mma") ? 2 : !strcmp(gp, "tc_m2") ? 3 : 0;
   c->magic = kMagic;
@@ -264,6 +266,34 @@ ztvm_status ztvm_int4_matmul_host(ztvm_ctx* ctx, const ztvm_mm_desc* d, void* y_
   return ZTVM_OK;
 }
 
+// Which grouped kernel serves a MoE launch: 0 none (per-pair GEMV), 1 tensor-core tiles, 2 streaming kernel.
+// `forced` is the context's ZTVM_MOE_GROUPED knob (-1 = by size).
+static int moe_pick(int forced, const ztvm_moe_desc* md, const ztvm::GemvParams& p, const void* y) {
+  const ztvm_mm_desc* d = &md->mm;
+  const uint64_t pairs = (uint64_t)md->tokens * md->slots;
+  const bool tiles_ok = (md->out_slot_stride | md->out_tok_stride) % 8 == 0 && aligned(y, 16) &&
+                        ztvm::moe_grouped_supported((int)d->bits, d->group, d->K, d->N, md->experts);
+  const bool stream_ok = ztvm::moe_tc_supported(p, (int)d->bits);
+  const bool few_per_expert = pairs < 24ull * md->experts;
+  if (forced == 1) return tiles_ok ? 1 : stream_ok ? 2 : 0;
+  if (forced == 2) return stream_ok ? 2 : tiles_ok ? 1 : 0;
+  return (stream_ok && (few_per_expert || !tiles_ok)) ? 2 : tiles_ok ? 1 : 0;
+}
+
+static ztvm::GemvParams moe_params(ztvm_ctx* ctx, const ztvm_moe_desc* md, void* y, const void* x, const void* scales,
+                                   const void* packed_w, const void* biases, const uint32_t* ids) {
+  ztvm_mm_desc dd = md->mm;
+  dd.M = 1;
+  ztvm::GemvParams p = gemv_params(&dd, y, x, scales, packed_w, biases);
+  p.ids = ids;
+  p.experts = md->experts;
+  p.in_slot_stride = md->in_slot_stride; p.out_slot_stride = md->out_slot_stride;
+  p.in_tok_stride = md->in_tok_stride; p.out_tok_stride = md->out_tok_stride;
+  p.ids_stride = md->ids_stride;
+  p.err_counter = ctx->err_counter;
+  return p;
+}
+
 ztvm_status ztvm_int4_matmul_moe(ztvm_ctx* ctx, const ztvm_moe_desc* md, void* y, const void* x, const void* scales,
                                  const void* packed_w, const void* biases, const uint32_t* ids, void* stream) {
   ztvm_status s = check_ctx(ctx);
@@ -285,25 +315,24 @@ ztvm_status ztvm_int4_matmul_moe(ztvm_ctx* ctx, const ztvm_moe_desc* md, void* y
   cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : ctx->stream;
   ztvm_mm_desc dd = *d;
   dd.M = 1;
-  // Many pairs: sort them by expert and run tensor-core tiles (each expert's weights dequantised once per 128 pairs).
+  // Many pairs: sort them by expert. While an expert sees only a few pairs the job is bound by streaming each active
+  // expert's weights once (streaming kernel); with many pairs per expert it is a real contraction (tensor-core tiles,
+  // each expert's weights dequantised once per 128 pairs).
   const uint64_t pairs = (uint64_t)md->tokens * md->slots;
-  const bool want_grouped = ctx->moe_grouped < 0 ? pairs >= 128 : ctx->moe_grouped == 1;
-  if (want_grouped && pairs < (1ull << 31) && (md->out_slot_stride | md->out_tok_stride) % 8 == 0 && aligned(y, 16) &&
-      ztvm::moe_grouped_supported((int)d->bits, d->group, d->K, d->N, md->experts)) {
-    const size_t need = ztvm::moe_grouped_scratch_bytes(md->experts, (uint32_t)pairs);
-    if (ctx->d_ws_bytes < need) {
-      ZTVM_CUDA(cudaDeviceSynchronize());
-      if ((s = grow(&ctx->d_ws, &ctx->d_ws_bytes, need, false))) return s;
+  const bool want_grouped = ctx->moe_grouped < 0 ? pairs >= 128 : ctx->moe_grouped >= 1;
+  if (want_grouped && pairs < (1ull << 31)) {
+    const ztvm::GemvParams p = moe_params(ctx, md, y, x, scales, packed_w, biases, ids);
+    const int pick = moe_pick(ctx->moe_grouped, md, p, y);
+    if (pick) {
+      const size_t need = ztvm::moe_grouped_scratch_bytes(md->experts, (uint32_t)pairs);
+      if (ctx->d_ws_bytes < need) {
+        ZTVM_CUDA(cudaDeviceSynchronize());
+        if ((s = grow(&ctx->d_ws, &ctx->d_ws_bytes, need, false))) return s;
+      }
+      if (pick == 2) ZTVM_CUDA(ztvm::launch_moe_tc(p, md->tokens, md->slots, static_cast<uint32_t*>(ctx->d_ws), ctx->sm_count, st));
+      else ZTVM_CUDA(ztvm::launch_moe_grouped(p, md->tokens, md->slots, static_cast<uint32_t*>(ctx->d_ws), ctx->err_counter + 1, st));
+      return ZTVM_OK;
     }
-    ztvm::GemvParams p = gemv_params(&dd, y, x, scales, packed_w, biases);
-    p.ids = ids;
-    p.experts = md->experts;
-    p.in_slot_stride = md->in_slot_stride; p.out_slot_stride = md->out_slot_stride;
-    p.in_tok_stride = md->in_tok_stride; p.out_tok_stride = md->out_tok_stride;
-    p.ids_stride = md->ids_stride;
-    p.err_counter = ctx->err_counter;
-    ZTVM_CUDA(ztvm::launch_moe_grouped(p, md->tokens, md->slots, static_cast<uint32_t*>(ctx->d_ws), ctx->err_counter + 1, st));
-    return ZTVM_OK;
   }
   // grid.y carries the token: split very long token lists into slabs of 65535
   for (uint32_t t0 = 0; t0 < md->tokens; t0 += 65535) {
@@ -346,23 +375,18 @@ ztvm_status ztvm_int4_matmul_moe_noalloc(ztvm_ctx* ctx, const ztvm_moe_desc* md,
                 "split the token list or call ztvm_int4_matmul_moe",
                 (unsigned long long)pairs, md->experts, (unsigned)ZTVM_MOE_NOALLOC_MAX_PAIRS,
                 (unsigned)ZTVM_MOE_NOALLOC_MAX_EXPERTS);
-  if (!ztvm::moe_grouped_supported((int)d->bits, d->group, d->K, d->N, md->experts))
-    return fail(ZTVM_ERR_UNSUPPORTED,
-                "this entry point runs the tensor-core tiles only: bits=4, group=64, K %% 64 == 0, N %% 128 == 0 "
-                "(got bits=%u group=%u K=%u N=%u)", d->bits, d->group, d->K, d->N);
-  if ((md->in_slot_stride | md->in_tok_stride | md->out_slot_stride | md->out_tok_stride) % 8 || !aligned(y, 16))
-    return fail(ZTVM_ERR_ALIGNMENT, "strides must be multiples of 8 elements and y 16-byte aligned");
+  if ((md->in_slot_stride | md->in_tok_stride) % 8)
+    return fail(ZTVM_ERR_ALIGNMENT, "input strides must be multiples of 8 elements (16-byte activation loads)");
   cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : ctx->stream;
-  ztvm_mm_desc dd = *d;
-  dd.M = 1;
-  ztvm::GemvParams p = gemv_params(&dd, y, x, scales, packed_w, biases);
-  p.ids = ids;
-  p.experts = md->experts;
-  p.in_slot_stride = md->in_slot_stride; p.out_slot_stride = md->out_slot_stride;
-  p.in_tok_stride = md->in_tok_stride; p.out_tok_stride = md->out_tok_stride;
-  p.ids_stride = md->ids_stride;
-  p.err_counter = ctx->err_counter;
-  ZTVM_CUDA(ztvm::launch_moe_grouped_static(p, md->tokens, md->slots, ctx->err_counter + 1, st));
+  const ztvm::GemvParams p = moe_params(ctx, md, y, x, scales, packed_w, biases, ids);
+  const int pick = moe_pick(ctx->moe_grouped, md, p, y);   // the same choice ztvm_int4_matmul_moe makes
+  if (!pick)
+    return fail(ZTVM_ERR_UNSUPPORTED,
+                "this entry point runs the grouped kernels only: bits=4, group=64, and either K %% 256 == 0, K <= 4096, "
+                "N %% 16 == 0 or K %% 64 == 0, N %% 128 == 0 with y 16-byte aligned and output strides multiples of 8 "
+                "(got bits=%u group=%u K=%u N=%u)", d->bits, d->group, d->K, d->N);
+  if (pick == 2) ZTVM_CUDA(ztvm::launch_moe_tc_static(p, md->tokens, md->slots, ctx->sm_count, st));
+  else ZTVM_CUDA(ztvm::launch_moe_grouped_static(p, md->tokens, md->slots, ctx->err_counter + 1, st));
   return ZTVM_OK;
 }
 

@@ -20,72 +20,14 @@
 //     __syncthreads per meeting, fixed summation order: results are deterministic).
 #include "ztvm_device.cuh"
 #include "ztvm_kernels.h"
+#include "ztvm_stream_mma.cuh"
 
 namespace ztvm {
 
-constexpr int kTcWarps = 16;
-constexpr int kTcDepth = 4;
-constexpr int kTcSlice = 256;                        // codes per warp slice = 128 B per row = 4 scale groups
-constexpr int kTcTileW = 16 * 128;                   // packed codes of one (tile, slice)
-constexpr int kTcTileBytes = kTcTileW + 16 * 16;     // + per row 4 scales, 4 biases (f16)
-constexpr int kTcRingBytes = kTcWarps * kTcDepth * kTcTileBytes;
 constexpr uint32_t kTcMaxAccBytes = 32 * 1024;       // cross-K-tile accumulators (only when K > 4096)
-
-__device__ __forceinline__ void tc_mma(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                       uint32_t b1, const float (&c)[4]) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
-      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
-}
-__device__ __forceinline__ void tc_cp16(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void tc_cp8(uint32_t dst, const void* src) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void tc_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ uint2 tc_lds64(uint32_t a) {
-  uint2 v;
-  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
-  return v;
-}
-__device__ __forceinline__ uint4 tc_lds128(uint32_t a) {
-  uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
-  return v;
-}
-
-// packed f32 pairs: sm_100 has a two-wide f32 FMA (fma.rn.f32x2), which halves the instructions of the group fold
-__device__ __forceinline__ unsigned long long tc_pk(float a, float b) {
-  unsigned long long r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
-  return r;
-}
-__device__ __forceinline__ float2 tc_unpk(unsigned long long v) {
-  float2 r;
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(r.x), "=f"(r.y) : "l"(v));
-  return r;
-}
-__device__ __forceinline__ unsigned long long tc_ffma2(unsigned long long a, unsigned long long b, unsigned long long c) {
-  unsigned long long d;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-  return d;
-}
-
 // rounds between two meetings: the partial buffers hold 2 x warps x rounds x 16 rows x NT floats
 __host__ __device__ constexpr int tc_rounds(int nt) { return nt <= 2 ? 4 : 2; }
 
-__device__ __forceinline__ uint32_t tc_lds32(uint32_t a) {
-  uint32_t v;
-  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
-  return v;
-}
-__device__ __forceinline__ uint32_t tc_lds16(uint32_t a) {
-  unsigned short v;
-  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
-  return v;
-}
 
 // NT = tokens padded to a power of two. The eight columns of an MMA are (group, token) pairs: with NT tokens one
 // accumulator collects GPA = 8 / NT scale groups side by side (the B fragment of a column is zero in the MMAs of the

@@ -49,11 +49,17 @@ size_t moe_grouped_scratch_bytes(uint32_t experts, uint32_t pairs);
 bool moe_grouped_supported(int bits, uint32_t group, uint32_t K, uint32_t N, uint32_t experts);
 cudaError_t launch_moe_grouped(const GemvParams& g, uint32_t tokens, uint32_t slots, uint32_t* scratch, uint32_t* status,
                                cudaStream_t st);
+// Streaming form of the grouped MoE matmul (ztvm_moe_tc.cu) for launches where an expert sees only a few pairs: bound
+// by reading each active expert's weights once. Same scratch as launch_moe_grouped.
+bool moe_tc_supported(const GemvParams& g, int bits);
+cudaError_t launch_moe_tc(const GemvParams& g, uint32_t tokens, uint32_t slots, uint32_t* scratch, int sm_count,
+                          cudaStream_t st);
 // The same launch with the planning scratch in a fixed array inside the module (no allocation anywhere on the path).
 // `moe_static_scratch_fits` says whether a problem fits that array; the launcher refuses one that does not.
 bool moe_static_scratch_fits(uint32_t experts, uint64_t pairs);
 cudaError_t launch_moe_grouped_static(const GemvParams& g, uint32_t tokens, uint32_t slots, uint32_t* status,
                                       cudaStream_t st);
+cudaError_t launch_moe_tc_static(const GemvParams& g, uint32_t tokens, uint32_t slots, int sm_count, cudaStream_t st);
 
 cudaError_t launch_unpack_codes(const uint32_t* W, uint8_t* codes, uint32_t N, uint32_t K, int bits, cudaStream_t st);
 cudaError_t launch_dequant(const uint32_t* W, const __half* S, const __half* B, void* out, uint32_t N, uint32_t K,

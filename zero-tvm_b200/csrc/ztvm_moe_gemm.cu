@@ -11,6 +11,7 @@
 #include <mutex>
 
 #include "ztvm_kernels.h"
+#include "ztvm_moe_plan.cuh"
 #include "ztvm_tc.cuh"
 
 namespace ztvm {
@@ -21,31 +22,6 @@ constexpr int kMoeWChunk = 4;
 constexpr int kMoeWorkWarps = 8;
 constexpr int kMoeThreads = 64 + kMoeWorkWarps * 32;
 constexpr int kMoeBM = 128, kMoeBN = 128;
-
-// scratch layout in 32-bit words
-struct MoeScratch {
-  uint32_t* counts;   // [E]
-  uint32_t* offsets;  // [E + 1]
-  uint32_t* cursor;   // [E]
-  uint32_t* ntiles;   // [1]
-  uint32_t* tiles;    // [max_tiles][3]: expert, first sorted row, rows
-  uint32_t* sorted;   // [P] pair index = token * slots + slot
-};
-__host__ __device__ inline size_t moe_scratch_words(uint32_t E, uint32_t P) {
-  const size_t max_tiles = (P + kMoeBM - 1) / kMoeBM + E;
-  return (size_t)E * 3 + 2 + 2 + max_tiles * 3 + P + 16;
-}
-__host__ __device__ inline MoeScratch moe_scratch_carve(uint32_t* base, uint32_t E, uint32_t P) {
-  MoeScratch s;
-  s.counts = base;
-  s.offsets = s.counts + E;
-  s.cursor = s.offsets + E + 1;
-  s.ntiles = s.cursor + E;
-  s.tiles = s.ntiles + 1;
-  const size_t max_tiles = (P + kMoeBM - 1) / kMoeBM + E;
-  s.sorted = s.tiles + max_tiles * 3;
-  return s;
-}
 
 __global__ void moe_count_kernel(const uint32_t* __restrict__ ids, uint32_t tokens, uint32_t slots, uint32_t ids_stride,
                                  uint32_t E, MoeScratch sc, uint32_t* err) {
@@ -58,7 +34,7 @@ __global__ void moe_count_kernel(const uint32_t* __restrict__ ids, uint32_t toke
   }
 }
 
-__global__ void moe_plan_kernel(uint32_t E, MoeScratch sc) {
+__global__ void moe_plan_kernel(uint32_t E, uint32_t tile_rows, MoeScratch sc) {
   __shared__ uint32_t tile_base[1025];
   if (threadIdx.x == 0) {
     uint32_t off = 0, tb = 0;
@@ -66,7 +42,7 @@ __global__ void moe_plan_kernel(uint32_t E, MoeScratch sc) {
       sc.offsets[e] = off;
       tile_base[e] = tb;
       off += sc.counts[e];
-      tb += (sc.counts[e] + kMoeBM - 1) / kMoeBM;
+      tb += (sc.counts[e] + tile_rows - 1) / tile_rows;
     }
     sc.offsets[E] = off;
     tile_base[E] = tb;
@@ -78,8 +54,8 @@ __global__ void moe_plan_kernel(uint32_t E, MoeScratch sc) {
     for (uint32_t j = 0; j < nt; ++j) {
       uint32_t* tt = sc.tiles + (size_t)(tile_base[e] + j) * 3;
       tt[0] = e;
-      tt[1] = sc.offsets[e] + j * kMoeBM;
-      tt[2] = min((uint32_t)kMoeBM, cnt - j * kMoeBM);
+      tt[1] = sc.offsets[e] + j * tile_rows;
+      tt[2] = min(tile_rows, cnt - j * tile_rows);
     }
   }
 }
@@ -317,6 +293,20 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_w, const MoeGemmPara
   if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
 }
 
+// Plan of one grouped launch: histogram of the expert ids, prefix sums + table of tiles of at most `tile_rows` pairs of
+// one expert, scatter of the pair indices into expert order. The words that must start at zero are cleared here.
+cudaError_t launch_moe_plan(const GemvParams& g, uint32_t tokens, uint32_t slots, const MoeScratch& sc, uint32_t tile_rows,
+                            cudaStream_t st) {
+  const uint32_t P = tokens * slots, E = g.experts;
+  cudaError_t e = cudaMemsetAsync(sc.counts, 0, ((size_t)E * 3 + 4) * 4, st);   // counts, offsets, cursor, ntiles
+  if (e != cudaSuccess) return e;
+  const unsigned blocks = (P + 255) / 256 > 1184 ? 1184 : (P + 255) / 256;
+  moe_count_kernel<<<blocks, 256, 0, st>>>(g.ids, tokens, slots, g.ids_stride, E, sc, g.err_counter);
+  moe_plan_kernel<<<1, 256, 0, st>>>(E, tile_rows, sc);
+  moe_scatter_kernel<<<blocks, 256, 0, st>>>(g.ids, tokens, slots, g.ids_stride, E, sc);
+  return cudaGetLastError();
+}
+
 // ---- host side -----------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -345,12 +335,8 @@ cudaError_t launch_moe_grouped(const GemvParams& g, uint32_t tokens, uint32_t sl
   if (!enc) return cudaErrorNotSupported;
   const uint32_t P = tokens * slots, E = g.experts;
   MoeScratch sc = moe_scratch_carve(scratch, E, P);
-  cudaError_t e = cudaMemsetAsync(scratch, 0, ((size_t)E * 3 + 4) * 4, st);   // counts, offsets, cursor, ntiles
+  cudaError_t e = launch_moe_plan(g, tokens, slots, sc, (uint32_t)kMoeBM, st);
   if (e != cudaSuccess) return e;
-  const unsigned blocks = (P + 255) / 256 > 1184 ? 1184 : (P + 255) / 256;
-  moe_count_kernel<<<blocks, 256, 0, st>>>(g.ids, tokens, slots, g.ids_stride, E, sc, g.err_counter);
-  moe_plan_kernel<<<1, 256, 0, st>>>(E, sc);
-  moe_scatter_kernel<<<blocks, 256, 0, st>>>(g.ids, tokens, slots, g.ids_stride, E, sc);
 
   CUtensorMap tmap_w;
   const cuuint64_t wdims[2] = {g.KP, (cuuint64_t)E * g.N};
@@ -387,9 +373,7 @@ cudaError_t launch_moe_grouped(const GemvParams& g, uint32_t tokens, uint32_t sl
 // or one that cannot afford the device-wide synchronisation that growing a buffer implies. The scratch lives in the
 // module's own image, so it exists (once per device) as soon as the module is loaded there.
 constexpr uint32_t kMoeStaticMaxExperts = 1024, kMoeStaticMaxPairs = 65536;
-constexpr size_t kMoeStaticWords = (size_t)kMoeStaticMaxExperts * 3 + 2 + 2 +
-                                   ((size_t)(kMoeStaticMaxPairs + kMoeBM - 1) / kMoeBM + kMoeStaticMaxExperts) * 3 +
-                                   kMoeStaticMaxPairs + 16;   // = moe_scratch_words(max experts, max pairs), 293 KB
+constexpr size_t kMoeStaticWords = moe_scratch_words(kMoeStaticMaxExperts, kMoeStaticMaxPairs);   // 385 KB
 static __device__ __align__(256) uint32_t g_moe_static_scratch[kMoeStaticWords];
 
 bool moe_static_scratch_fits(uint32_t experts, uint64_t pairs) {
@@ -428,6 +412,14 @@ cudaError_t launch_moe_grouped_static(const GemvParams& g, uint32_t tokens, uint
   // launch_moe_grouped zeroes the words that must start at zero (counts, offsets, cursors, tile count) on `st`
   // before the planning kernels; the rest of the scratch is fully written before it is read.
   return launch_moe_grouped(g, tokens, slots, scratch, status, st);
+}
+
+cudaError_t launch_moe_tc_static(const GemvParams& g, uint32_t tokens, uint32_t slots, int sm_count, cudaStream_t st) {
+  if (!moe_static_scratch_fits(g.experts, (uint64_t)tokens * slots)) return cudaErrorInvalidValue;
+  uint32_t* scratch = nullptr;
+  const cudaError_t e = moe_static_scratch_ptr(&scratch);
+  if (e != cudaSuccess) return e;
+  return launch_moe_tc(g, tokens, slots, scratch, sm_count, st);   // its plan launch clears what must start at zero
 }
 
 }  // namespace ztvm
