@@ -16,7 +16,8 @@ Workloads
   layer_set_nshard   the same eight projections with their output rows sharded over the ranks and one all-gather
                      per projection (strong scaling, GB/s of the whole layer set); --m-rows 1|4
   moe_ep             35B-A3B-class MoE block (256 experts + shared, hidden 2048, ffn 512, top-8), experts sharded
-                     over the ranks, all-to-all dispatch / combine (strong scaling, TFLOP/s); --tokens T
+                     over the ranks, all-to-all dispatch / combine (TFLOP/s); --tokens T per rank (--ep-scaling weak,
+                     default) or in total (--ep-scaling strong)
 
 With N > 1 the first three workloads run as independent replicas, one per rank, on their own weight sets (a single
 GEMM / GEMV does not shard); value is the aggregate over ranks divided by the slowest rank's device time.
@@ -214,7 +215,7 @@ def run_sharded(args, rank, world, local):
             W, sc, b = rand_w((), N, K)
             lo, hi = sharded.shard_rows(N, world, rank)
             projs.append(sharded.NShardedProjection(k, W[lo:hi].contiguous(), sc[lo:hi].contiguous(), b[lo:hi].contiguous(),
-                                                    N, K, out_f32=f32))
+                                                    N, K, out_f32=f32, fused=args.nshard_gather == "fused", max_m=max(1, M)))
             xs.append(torch.randn((M, K), device=device, generator=g).to(torch.float16))
             total_bytes += algorithmic_bytes(N, K, M, out_bytes=4 if f32 else 2)
             if name == "k_proj" and rank == 0:
@@ -232,7 +233,7 @@ def run_sharded(args, rank, world, local):
                 pj.forward(x, M)
         units, unit, launches = total_bytes / 1e9, "GB/s", len(projs)
         cfg = {"workload": args.workload, "M": M, "shapes": [n for n, *_ in z.synth.DENSE_LAYER_SET],
-               "parallelism": f"output rows / {world} + all-gather", "l2": "inputs larger than L2: 459 MB of weights per step"}
+               "parallelism": f"output rows / {world} + " + ("peer stores from the GEMV + barrier" if args.nshard_gather == "fused" and world > 1 else "all-gather"), "l2": "inputs larger than L2: 459 MB of weights per step"}
         bound, peak = "hbm", measured_peaks()["hbm"] * world
     else:
         E, top_k, d, ffn, T = 256, 8, 2048, 512, args.tokens
@@ -244,7 +245,7 @@ def run_sharded(args, rank, world, local):
             stacks.append((W[sel].contiguous(), sc[sel].contiguous(), b[sel].contiguous()))
             del W, sc, b
         moe = sharded.ExpertParallelMoE(k, *stacks, E=E, top_k=top_k, d=d, ffn=ffn)
-        tl = max(1, T // world)
+        tl = T if args.ep_scaling == "weak" else max(1, T // world)   # weak: --tokens is per rank
         x = torch.randn((tl, d), device=device).to(torch.float16)
         logits = torch.randn((tl, E + 1), device=device)
 
@@ -252,20 +253,40 @@ def run_sharded(args, rank, world, local):
             moe.forward(x, logits)
         pairs = tl * world * (top_k + 1)
         units, unit, launches = pairs * 3 * 2.0 * ffn * d / 1e12, "TFLOP/s", 9
-        cfg = {"workload": args.workload, "tokens": tl * world, "experts": E, "top_k": top_k, "hidden": d, "ffn": ffn,
+        cfg = {"workload": args.workload, "tokens": tl * world, "tokens_per_rank": tl, "ep_scaling": args.ep_scaling, "experts": E, "top_k": top_k, "hidden": d, "ffn": ffn,
                "parallelism": f"experts / {world} + all-to-all", "l2": "inputs larger than L2: 455 MB of expert weights"}
         bound, peak = "hbm", measured_peaks()["hbm"] * world
     for _ in range(args.warmup):
         step()
     torch.cuda.synchronize()
+    # The row-sharded layer set is pure kernel launches (GEMV with peer stores + barrier kernel, or one GPU): replay it
+    # from a CUDA graph so the host's launch cost does not enter the device-timed number. The NCCL and the MoE forms
+    # need the host between launches (split sizes) and run eagerly.
+    replay = None
+    if args.workload == "layer_set_nshard" and (world == 1 or args.nshard_gather == "fused"):
+        side = torch.cuda.Stream(device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step(); step()                      # both output buffers seen once on the capture stream
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                step(); step()                  # an even number: the double buffers end where they started
+            side.synchronize()
+        replay = graph
+        cfg["launch"] = "CUDA graph of two steps"
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local) as clocks:
         ev0.record()
-        for _ in range(args.steps):
-            step()
+        if replay is not None:
+            for _ in range((args.steps + 1) // 2):
+                replay.replay()
+        else:
+            for _ in range(args.steps):
+                step()
         ev1.record()
         torch.cuda.synchronize()
     if world > 1:
@@ -276,10 +297,11 @@ def run_sharded(args, rank, world, local):
         t = torch.tensor([ms], device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
-    ms_per_step = ms / args.steps
+    ms_per_step = ms / (2 * ((args.steps + 1) // 2) if replay is not None else args.steps)
     value = units / (ms_per_step * 1e-3)
     out = {"metric": METRIC, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-           "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+           "ms_per_step": ms_per_step, "higher_is_better": True,
+           "scaling": "weak" if (args.workload == "moe_ep" and args.ep_scaling == "weak") else "strong", "vs_baseline": None,
            "dtype": "f16 x int4 -> f32 accumulate", "data": "synthetic", "config": cfg,
            "gpu_launches": int(args.steps * launches), "clocks": clocks.summary(), "verified": verified}
     if unit == "GB/s":
@@ -301,7 +323,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--m-rows", type=int, default=1, help="activation rows of layer_set_nshard")
-    ap.add_argument("--tokens", type=int, default=2048, help="tokens of moe_ep (whole job)")
+    ap.add_argument("--tokens", type=int, default=2048, help="tokens of moe_ep: per rank (weak) or whole job (strong)")
+    ap.add_argument("--ep-scaling", default="weak", choices=["weak", "strong"])
+    ap.add_argument("--nshard-gather", default="fused", choices=["fused", "nccl"],
+                    help="layer_set_nshard: shards meet by peer stores from the GEMV + a barrier, or by NCCL all-gather")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     rank = int(os.environ.get("RANK", "0"))

@@ -92,6 +92,18 @@ typedef struct ztvm_mm_desc {
 ZTVM_API ztvm_status ztvm_int4_matmul(ztvm_ctx* ctx, const ztvm_mm_desc* desc, void* y, const void* x,
                              const void* scales, const void* packed_w, const void* biases, void* stream);
 
+/* The decode matmul (M <= 8) with its [M, N] result written to n_dst destinations at once, rows y_row_stride
+ * elements apart. This is the primitive of the row-sharded form: rank r owns N of a projection's N_total output
+ * rows and stores its shard straight into every rank's full output (the other ranks' buffers are peer-mapped
+ * device addresses: the stores travel over NVLink from inside the kernel, there is no separate all-gather).
+ * Each y_dsts[i] points at the shard's first column inside destination i. The reference runs on one device and
+ * has no counterpart; single-device callers use ztvm_int4_matmul. Ordering between ranks (that every shard has
+ * arrived before anyone reads the full row) is the caller's: a barrier after the call.
+ * Only the persistent GEMV serves this form: bits 4, group 64, K % 256 == 0, else ZTVM_ERR_UNSUPPORTED. */
+ZTVM_API ztvm_status ztvm_int4_matmul_multi(ztvm_ctx* ctx, const ztvm_mm_desc* desc, void* const* y_dsts,
+                                   uint32_t n_dst, uint32_t y_row_stride, const void* x, const void* scales,
+                                   const void* packed_w, const void* biases, void* stream);
+
 /* Same call with HOST activations and HOST output: copies x to the device, runs, copies y back and
  * waits. Weights, scales and biases stay device-resident, as they are in the engine
  * (src/zero-tvm/engine-core.ts:5259-5267). Synchronous. */

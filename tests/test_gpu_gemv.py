@@ -252,3 +252,24 @@ def test_host_buffer_entry_point(backend, dev, oracle_c):
     backend.ctx.int4_matmul_host(d, y, np.ascontiguousarray(p["x"]), dev.put(p["scales"]), dev.put(p["W"]),
                                  dev.put(p["biases"]))
     check_y(y, p, oracle_c)
+
+
+def test_multi_destination_matmul_matches_the_single_destination_call(backend, dev, oracle_c):
+    """ztvm_int4_matmul_multi: the shard [M, N] lands at a column offset inside three wider outputs (stand-ins for the
+    ranks' full outputs), bit-identical to ztvm_int4_matmul, and nothing else in those outputs is touched."""
+    N, K, M, N_total, lo = 1024, 2048, 4, 2560, 512
+    p = z.synth.projection(N, K, M=M, seed=5)
+    W, s, b, x = (dev.put(p[k]) for k in ("W", "scales", "biases", "x"))
+    y_ref = dev.empty((M, N), np.float16)
+    backend.ctx.int4_matmul(z.MmDesc(K, N, M, 64, 4, 1, 0), y_ref, x, s, W, b)
+    outs = [dev.empty((M, N_total), np.float16, fill=3.0) for _ in range(3)]
+    backend.ctx.int4_matmul_multi(z.MmDesc(K, N, M, 64, 4, 1, 0), [o.data_ptr() + lo * 2 for o in outs], N_total, x, s, W, b)
+    backend.ctx.sync()
+    ref = dev.get(y_ref).view(np.uint16)
+    for o in outs:
+        got = dev.get(o)
+        assert np.array_equal(got[:, lo:lo + N].view(np.uint16), ref)
+        assert (got[:, :lo] == 3.0).all() and (got[:, lo + N:] == 3.0).all()
+    with pytest.raises(z.ZtvmError) as e:   # shapes the persistent GEMV does not take are refused, not rerouted
+        backend.ctx.int4_matmul_multi(z.MmDesc(K, N, 16, 64, 4, 1, 0), [outs[0]], N_total, x, s, W, b)
+    assert e.value.status == z.capi.ERR_UNSUPPORTED

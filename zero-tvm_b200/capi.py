@@ -14,7 +14,7 @@ LIB_PATH = os.path.join(_HERE, "lib", "libztvm_b200.so")
 # every symbol include/ztvm_b200.h declares
 SYMBOLS = [
     "ztvm_version", "ztvm_status_string", "ztvm_init", "ztvm_destroy", "ztvm_last_error", "ztvm_sync",
-    "ztvm_int4_matmul", "ztvm_int4_matmul_host", "ztvm_int4_matmul_moe", "ztvm_int4_matmul_moe_noalloc",
+    "ztvm_int4_matmul", "ztvm_int4_matmul_multi", "ztvm_int4_matmul_host", "ztvm_int4_matmul_moe", "ztvm_int4_matmul_moe_noalloc",
     "ztvm_moe_route_topk", "ztvm_silu_mul",
     "ztvm_moe_combine", "ztvm_unpack_codes", "ztvm_dequant", "ztvm_device_errors",
 ]
@@ -61,6 +61,7 @@ def load() -> C.CDLL:
         "ztvm_destroy": [vp],
         "ztvm_sync": [vp],
         "ztvm_int4_matmul": [vp, C.POINTER(MmDesc), vp, vp, vp, vp, vp, vp],
+        "ztvm_int4_matmul_multi": [vp, C.POINTER(MmDesc), C.POINTER(C.c_void_p), u32, u32, vp, vp, vp, vp, vp],
         "ztvm_int4_matmul_host": [vp, C.POINTER(MmDesc), vp, vp, vp, vp, vp],
         "ztvm_int4_matmul_moe": [vp, C.POINTER(MoeDesc), vp, vp, vp, vp, vp, vp, vp],
         "ztvm_int4_matmul_moe_noalloc": [vp, C.POINTER(MoeDesc), vp, vp, vp, vp, vp, vp, vp],
@@ -137,6 +138,13 @@ class Context:
     def int4_matmul_host(self, desc: MmDesc, y_host, x_host, scales, packed_w, biases=None):
         check(self._lib.ztvm_int4_matmul_host(self.handle, C.byref(desc), ptr(y_host), ptr(x_host), ptr(scales),
                                               ptr(packed_w), ptr(biases)))
+
+    def int4_matmul_multi(self, desc: MmDesc, y_dsts, y_row_stride, x, scales, packed_w, biases=None, stream=None):
+        """Decode matmul whose result goes to every address in `y_dsts` (ints or tensors; peers' buffers included)."""
+        addrs = [d if isinstance(d, int) else d.data_ptr() for d in y_dsts]
+        arr = (C.c_void_p * len(addrs))(*addrs)
+        check(self._lib.ztvm_int4_matmul_multi(self.handle, C.byref(desc), arr, len(addrs), y_row_stride, ptr(x),
+                                               ptr(scales), ptr(packed_w), ptr(biases), stream_ptr(stream)))
 
     def int4_matmul_moe(self, desc: MoeDesc, y, x, scales, packed_w, biases, ids, stream=None):
         check(self._lib.ztvm_int4_matmul_moe(self.handle, C.byref(desc), ptr(y), ptr(x), ptr(scales),

@@ -246,6 +246,32 @@ ztvm_status ztvm_int4_matmul(ztvm_ctx* ctx, const ztvm_mm_desc* d, void* y, cons
   return ZTVM_OK;
 }
 
+ztvm_status ztvm_int4_matmul_multi(ztvm_ctx* ctx, const ztvm_mm_desc* d, void* const* y_dsts, uint32_t n_dst,
+                                   uint32_t y_row_stride, const void* x, const void* scales, const void* packed_w,
+                                   const void* biases, void* stream) {
+  ztvm_status s = check_ctx(ctx);
+  if (s) return s;
+  if ((s = check_desc(d, true))) return s;
+  if (!y_dsts) return fail(ZTVM_ERR_NULL_POINTER, "y_dsts is NULL");
+  if (n_dst < 1 || n_dst > 8) return fail(ZTVM_ERR_BAD_DIMS, "n_dst=%u must be 1..8", n_dst);
+  for (uint32_t i = 0; i < n_dst; ++i)
+    if (!y_dsts[i]) return fail(ZTVM_ERR_NULL_POINTER, "y_dsts[%u] is NULL", i);
+  if ((s = check_buffers(d, y_dsts[0], x, scales, packed_w, biases))) return s;
+  if (d->M > 8) return fail(ZTVM_ERR_UNSUPPORTED, "the multi-destination form is the decode GEMV: M=%u exceeds 8", d->M);
+  if (y_row_stride < d->N) return fail(ZTVM_ERR_BAD_DIMS, "y_row_stride=%u < N=%u", y_row_stride, d->N);
+  cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : ctx->stream;
+  ztvm::GemvParams p = gemv_params(d, y_dsts[0], x, scales, packed_w, biases);
+  p.y_row_stride = y_row_stride;
+  p.n_more = n_dst - 1;
+  for (uint32_t i = 1; i < n_dst; ++i) p.y_more[i - 1] = y_dsts[i];
+  if (!ztvm::gemv_tc_supported(p, (int)d->bits, ctx->sm_count))
+    return fail(ZTVM_ERR_UNSUPPORTED,
+                "the multi-destination form runs the persistent GEMV only: bits=4, group=64, K %% 256 == 0, 16-byte aligned "
+                "x and weights (got bits=%u group=%u K=%u)", d->bits, d->group, d->K);
+  ZTVM_CUDA(ztvm::launch_gemv_tc(p, ctx->sm_count, st));
+  return ZTVM_OK;
+}
+
 ztvm_status ztvm_int4_matmul_host(ztvm_ctx* ctx, const ztvm_mm_desc* d, void* y_host, const void* x_host,
                                   const void* scales, const void* packed_w, const void* biases) {
   ztvm_status s = check_ctx(ctx);

@@ -267,8 +267,14 @@ gemv_tc_kernel(const GemvParams p) {
           if (kt + 1 < num_kt) { *a = v; continue; }
         }
         const size_t o = (size_t)tok * p.y_row_stride + r0 + row;
-        if (p.out_f32) reinterpret_cast<float*>(p.Y)[o] = v;
-        else reinterpret_cast<__half*>(p.Y)[o] = __float2half_rn(v);
+        if (p.out_f32) {
+          reinterpret_cast<float*>(p.Y)[o] = v;
+          for (uint32_t k2 = 0; k2 < p.n_more; ++k2) reinterpret_cast<float*>(p.y_more[k2])[o] = v;   // peers (NVLink stores)
+        } else {
+          const __half hv = __float2half_rn(v);
+          reinterpret_cast<__half*>(p.Y)[o] = hv;
+          for (uint32_t k2 = 0; k2 < p.n_more; ++k2) reinterpret_cast<__half*>(p.y_more[k2])[o] = hv;
+        }
       }
     }
   }

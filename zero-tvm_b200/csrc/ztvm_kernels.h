@@ -23,6 +23,9 @@ struct GemvParams {
   const uint32_t* ids;
   uint32_t experts, in_slot_stride, out_slot_stride, in_tok_stride, out_tok_stride, ids_stride;
   uint32_t* err_counter;
+  // further destinations of the output (same layout as Y): peers' copies of a sharded projection's result
+  void* y_more[7];
+  uint32_t n_more;
 };
 
 cudaError_t launch_gemv(GemvParams p, int bits, bool moe, uint32_t tokens, uint32_t slots, int sm_count,

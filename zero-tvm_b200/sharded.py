@@ -52,6 +52,12 @@ class CudaKernels:
         entry = resolve_matmul(affine=True, K=K, out_f32=out_f32) if M == 1 else "int4_matmul_batched_dyn_affine"
         self.be.dispatch(entry, [y, x, s, W, pod_args(K, N, m_rows=None if M == 1 else M), b], stream=self._stream())
 
+    def matmul_multi(self, y_dsts, y_row_stride, x, W, s, b, N, K, M, out_f32=False):
+        """The decode matmul with its [M, N] result stored into every address of `y_dsts` (ztvm_int4_matmul_multi)."""
+        from .capi import MmDesc
+        self.be.ctx.int4_matmul_multi(MmDesc(K, N, M, 64, 4, 1, int(out_f32)), y_dsts, y_row_stride, x, s, W, b,
+                                      stream=self._stream())
+
     def route_topk(self, ids, scores, logits, E, K, tokens):
         self.be.moe_router_topk(ids, scores, logits, E, K, True, True, tokens, stream=self._stream())
 
@@ -77,9 +83,19 @@ class CudaKernels:
 
 
 class NShardedProjection:
-    """One dense projection with its output rows split over the ranks of `group`."""
+    """One dense projection with its output rows split over the ranks of `group`.
 
-    def __init__(self, kernels, W, scales, biases, N_total: int, K: int, *, out_f32: bool = False, group=None):
+    Two ways for the shards to meet:
+      fused=False  each rank computes its [M, per] block, one NCCL all-gather assembles the rows (any M);
+      fused=True   decode form (M <= max_m <= 8): every rank holds the full output in symmetric memory and the GEMV of
+                   rank r stores its shard into ALL ranks' outputs from inside the kernel (peer stores over NVLink),
+                   followed by one symmetric-memory barrier. No collective kernel, no staging copy. The outputs are
+                   double-buffered: the tensor returned by forward() is overwritten by the second forward() after it,
+                   so consume it (in stream order) before that.
+    """
+
+    def __init__(self, kernels, W, scales, biases, N_total: int, K: int, *, out_f32: bool = False, group=None,
+                 fused: bool = False, max_m: int = 8):
         self.k, self.group = kernels, group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -88,9 +104,31 @@ class NShardedProjection:
         self.per = shard_rows(N_total, self.world, 0)[1]
         assert W.shape[0] == self.hi - self.lo, "pass this rank's row shard"
         self.W, self.s, self.b = W, scales, biases
+        self.fused = bool(fused) and self.world > 1
+        if self.fused:
+            import torch.distributed._symmetric_memory as symm
+            assert 1 <= max_m <= 8
+            dt = torch.float32 if out_f32 else torch.float16
+            self.max_m, self._flip = max_m, 0
+            self._out = symm.empty((2, max_m, N_total), dtype=dt, device=W.device)
+            g = group if group is not None else dist.group.WORLD
+            self._hdl = symm.rendezvous(self._out, g.group_name)
+            esz = 4 if out_f32 else 2
+            # address of (buffer b, row 0, column lo) inside every rank's copy
+            self._dst = [[int(base) + (bi * max_m * N_total + self.lo) * esz for base in self._hdl.buffer_ptrs]
+                         for bi in range(2)]
 
     def forward(self, x: torch.Tensor, M: int) -> torch.Tensor:
         """x f16 [M, K] (replicated) -> y [M, N_total], every rank holding the whole output."""
+        if self.fused:
+            assert M <= self.max_m
+            bi = self._flip
+            self._flip ^= 1
+            if self.hi > self.lo:
+                self.k.matmul_multi(self._dst[bi], self.N_total, x, self.W, self.s, self.b, self.hi - self.lo, self.K, M,
+                                    self.out_f32)
+            self._hdl.barrier(channel=bi)          # every shard has landed everywhere (runs on the current stream)
+            return self._out[bi, :M]
         dt = torch.float32 if self.out_f32 else torch.float16
         n_loc = self.hi - self.lo
         # every rank contributes a [M, per] block (the last shard may be short: padded, trimmed after the gather)
