@@ -231,3 +231,19 @@ def test_moe_argument_errors(backend, dev):
             call(**kw)
         assert e.value.status == code, (kw, e.value)
     call(tokens=0)   # empty token list is a no-op, not an error
+
+
+@pytest.mark.parametrize("T", [3, 200])
+def test_expert_parallel_form_on_one_rank_matches_the_seven_dispatches(T, backend, dev):
+    """sharded.ExpertParallelMoE with the CUDA kernels and a single rank (no process group): same block, other
+    kernels (sorted pairs, dense shared expert), so agreement is to the whole-block bound, not bit for bit."""
+    import torch
+    from zero_tvm_b200 import sharded
+    mb = z.synth.moe_block(T, E=16, hidden=512, ffn=256, seed=31)
+    ref = run_block(backend, dev, mb, K_top=4)["y"].astype(np.float64)
+    stacks = [tuple(dev.put(a) for a in mb[n]) for n in ("gate", "up", "down")]
+    moe = sharded.ExpertParallelMoE(sharded.CudaKernels(backend), *stacks, E=16, top_k=4, d=512, ffn=256)
+    y = moe.forward(dev.put(mb["x"]), dev.put(mb["logits"]))
+    torch.cuda.synchronize()
+    got = y.cpu().numpy().astype(np.float64)
+    assert np.abs(got - ref).max() <= 5e-3 * np.abs(ref).max()

@@ -49,6 +49,11 @@ class OracleKernels:
         self.zc.moe_gemv_ref(h, *st(down), ids, d, ffn, 64, 4, ffn, d, ffn, d, out.reshape(-1))
         y_rows.copy_(torch.from_numpy(out))
 
+    def dense_ffn(self, x, gate, up, down, e, d, ffn, rows):
+        y = torch.empty((rows, d), dtype=torch.float16)
+        self.expert_ffn(y, x, torch.full((rows, 1), e, dtype=torch.int32), gate, up, down, d, ffn, rows)
+        return y
+
     def combine(self, out, y_slots, scores, tokens, slots, d):
         out.copy_(torch.from_numpy(self.zc.moe_combine(self._np(y_slots), self._np(scores))))
 

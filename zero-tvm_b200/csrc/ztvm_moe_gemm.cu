@@ -34,29 +34,88 @@ __global__ void moe_count_kernel(const uint32_t* __restrict__ ids, uint32_t toke
   }
 }
 
-__global__ void moe_plan_kernel(uint32_t E, uint32_t tile_rows, MoeScratch sc) {
-  __shared__ uint32_t tile_base[1025];
-  if (threadIdx.x == 0) {
-    uint32_t off = 0, tb = 0;
-    for (uint32_t e = 0; e < E; ++e) {
-      sc.offsets[e] = off;
-      tile_base[e] = tb;
-      off += sc.counts[e];
-      tb += (sc.counts[e] + tile_rows - 1) / tile_rows;
+// Exclusive scan over the 1024 threads of a block (values in registers, one per thread).
+__device__ __forceinline__ uint32_t moe_block_excl_scan(uint32_t v, uint32_t* warp_sums, uint32_t* total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint32_t inc = v;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const uint32_t t = __shfl_up_sync(0xffffffffu, inc, d);
+    if (lane >= d) inc += t;
+  }
+  if (lane == 31) warp_sums[warp] = inc;
+  __syncthreads();
+  if (warp == 0) {
+    uint32_t w = warp_sums[lane];
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const uint32_t t = __shfl_up_sync(0xffffffffu, w, d);
+      if (lane >= d) w += t;
     }
-    sc.offsets[E] = off;
-    tile_base[E] = tb;
-    *sc.ntiles = tb;
+    warp_sums[lane] = w;   // inclusive over warps
   }
   __syncthreads();
-  for (uint32_t e = threadIdx.x; e < E; e += blockDim.x) {
-    const uint32_t cnt = sc.counts[e], nt = tile_base[e + 1] - tile_base[e];
-    for (uint32_t j = 0; j < nt; ++j) {
-      uint32_t* tt = sc.tiles + (size_t)(tile_base[e] + j) * 3;
-      tt[0] = e;
-      tt[1] = sc.offsets[e] + j * tile_rows;
-      tt[2] = min(tile_rows, cnt - j * tile_rows);
-    }
+  const uint32_t base = warp ? warp_sums[warp - 1] : 0u;
+  *total = warp_sums[31];
+  __syncthreads();         // warp_sums may be reused by the next scan
+  return base + inc - v;
+}
+
+// One block of 1024 threads, thread e = expert e (E <= 1024): offsets and tile table from the counts.
+__global__ void __launch_bounds__(1024) moe_plan_kernel(uint32_t E, uint32_t tile_rows, MoeScratch sc) {
+  __shared__ uint32_t warp_sums[32];
+  const uint32_t e = threadIdx.x;
+  const uint32_t cnt = e < E ? sc.counts[e] : 0u;
+  const uint32_t nt = (cnt + tile_rows - 1) / tile_rows;
+  uint32_t total_pairs, total_tiles;
+  const uint32_t off = moe_block_excl_scan(cnt, warp_sums, &total_pairs);
+  const uint32_t tb = moe_block_excl_scan(nt, warp_sums, &total_tiles);
+  if (e < E) sc.offsets[e] = off;
+  if (e == 0) { sc.offsets[E] = total_pairs; *sc.ntiles = total_tiles; }
+  for (uint32_t j = 0; j < nt; ++j) {
+    uint32_t* tt = sc.tiles + (size_t)(tb + j) * 3;
+    tt[0] = e;
+    tt[1] = off + j * tile_rows;
+    tt[2] = min(tile_rows, cnt - j * tile_rows);
+  }
+}
+
+// The whole plan in ONE block for short pair lists: histogram and cursors in shared memory, same scans, same tables.
+__global__ void __launch_bounds__(1024) moe_plan_small_kernel(const uint32_t* __restrict__ ids, uint32_t tokens, uint32_t slots,
+                                                              uint32_t ids_stride, uint32_t E, uint32_t tile_rows,
+                                                              MoeScratch sc, uint32_t* err) {
+  __shared__ uint32_t cnt_sm[1024], cur_sm[1024], warp_sums[32];
+  const uint32_t e = threadIdx.x, P = tokens * slots;
+  cnt_sm[e] = 0u;
+  __syncthreads();
+  uint32_t bad = 0;
+  for (uint32_t i = threadIdx.x; i < P; i += blockDim.x) {
+    const uint32_t t = i / slots, s = i - t * slots;
+    const uint32_t x = ids[(size_t)t * ids_stride + s];
+    if (x < E) atomicAdd(&cnt_sm[x], 1u);
+    else ++bad;
+  }
+  if (bad) atomicAdd(err, bad);
+  __syncthreads();
+  const uint32_t cnt = e < E ? cnt_sm[e] : 0u;
+  const uint32_t nt = (cnt + tile_rows - 1) / tile_rows;
+  uint32_t total_pairs, total_tiles;
+  const uint32_t off = moe_block_excl_scan(cnt, warp_sums, &total_pairs);
+  const uint32_t tb = moe_block_excl_scan(nt, warp_sums, &total_tiles);
+  cur_sm[e] = off;
+  if (e < E) { sc.counts[e] = cnt; sc.offsets[e] = off; }
+  if (e == 0) { sc.offsets[E] = total_pairs; *sc.ntiles = total_tiles; }
+  for (uint32_t j = 0; j < nt; ++j) {
+    uint32_t* tt = sc.tiles + (size_t)(tb + j) * 3;
+    tt[0] = e;
+    tt[1] = off + j * tile_rows;
+    tt[2] = min(tile_rows, cnt - j * tile_rows);
+  }
+  __syncthreads();
+  for (uint32_t i = threadIdx.x; i < P; i += blockDim.x) {
+    const uint32_t t = i / slots, s = i - t * slots;
+    const uint32_t x = ids[(size_t)t * ids_stride + s];
+    if (x < E) sc.sorted[atomicAdd(&cur_sm[x], 1u)] = i;
   }
 }
 
@@ -298,11 +357,15 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_w, const MoeGemmPara
 cudaError_t launch_moe_plan(const GemvParams& g, uint32_t tokens, uint32_t slots, const MoeScratch& sc, uint32_t tile_rows,
                             cudaStream_t st) {
   const uint32_t P = tokens * slots, E = g.experts;
+  if (P <= 4096) {   // short lists: one block does it all, nothing to clear beforehand
+    moe_plan_small_kernel<<<1, 1024, 0, st>>>(g.ids, tokens, slots, g.ids_stride, E, tile_rows, sc, g.err_counter);
+    return cudaGetLastError();
+  }
   cudaError_t e = cudaMemsetAsync(sc.counts, 0, ((size_t)E * 3 + 4) * 4, st);   // counts, offsets, cursor, ntiles
   if (e != cudaSuccess) return e;
   const unsigned blocks = (P + 255) / 256 > 1184 ? 1184 : (P + 255) / 256;
   moe_count_kernel<<<blocks, 256, 0, st>>>(g.ids, tokens, slots, g.ids_stride, E, sc, g.err_counter);
-  moe_plan_kernel<<<1, 256, 0, st>>>(E, tile_rows, sc);
+  moe_plan_kernel<<<1, 1024, 0, st>>>(E, tile_rows, sc);
   moe_scatter_kernel<<<blocks, 256, 0, st>>>(g.ids, tokens, slots, g.ids_stride, E, sc);
   return cudaGetLastError();
 }

@@ -78,6 +78,26 @@ class CudaKernels:
         self.be.dispatch(ent_d, [y_rows, h, down[1], down[0], moe_down_pod_args(d, ffn, 1), down[2], local_ids],
                          (d // 4, rows, 1), stream=st)
 
+    def dense_ffn(self, x, gate, up, down, e, d, ffn, rows):
+        """down_e(silu(gate_e x) * up_e x) for every row of x with ONE expert e of the stacks: plain projections."""
+        dev = x.device
+        gu = torch.empty((rows, 2 * ffn), dtype=torch.float16, device=dev)
+        g = torch.empty((rows, ffn), dtype=torch.float16, device=dev)
+        u = torch.empty((rows, ffn), dtype=torch.float16, device=dev)
+        for m0 in range(0, rows, 4096):                      # the batched entry takes at most 65535 rows per call
+            m = min(4096, rows - m0)
+            self.matmul(g[m0:m0 + m], x[m0:m0 + m], gate[0][e], gate[1][e], gate[2][e], ffn, d, m)
+            self.matmul(u[m0:m0 + m], x[m0:m0 + m], up[0][e], up[1][e], up[2][e], ffn, d, m)
+        gu[:, :ffn] = g
+        gu[:, ffn:] = u
+        h = torch.empty((rows, ffn), dtype=torch.float16, device=dev)
+        self.be.silu_mul(h, gu, rows, ffn, stream=self._stream())
+        y = torch.empty((rows, d), dtype=torch.float16, device=dev)
+        for m0 in range(0, rows, 4096):
+            m = min(4096, rows - m0)
+            self.matmul(y[m0:m0 + m], h[m0:m0 + m], down[0][e], down[1][e], down[2][e], d, ffn, m)
+        return y
+
     def combine(self, out, y_slots, scores, tokens, slots, d):
         self.be.moe_combine(out, y_slots, scores, tokens, slots, d, stream=self._stream())
 
@@ -213,11 +233,8 @@ class ExpertParallelMoE:
         routed = torch.empty((T * K, d), dtype=torch.float16, device=dev)
         routed.index_copy_(0, plan.order, y_back)
         y_slots[:, :K] = routed.view(T, K, d)
-        # the shared expert is replicated: its slot is computed where the token lives
-        y_sh = torch.empty((T, d), dtype=torch.float16, device=dev)
-        shared_idx = torch.full((T, 1), self.epr, dtype=torch.int32, device=dev)
-        self.k.expert_ffn(y_sh, x, shared_idx, self.gate, self.up, self.down, d, self.ffn, T)
-        y_slots[:, K] = y_sh
+        # the shared expert is replicated and sees every local token: three dense projections (GEMM / GEMV by T), no ids
+        y_slots[:, K] = self.k.dense_ffn(x, self.gate, self.up, self.down, self.epr, d, self.ffn, T)
         out = torch.empty((T, d), dtype=torch.float16, device=dev)
         self.k.combine(out, y_slots, scores, T, K + 1, d)
         return out
