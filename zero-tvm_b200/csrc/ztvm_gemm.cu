@@ -23,8 +23,8 @@
 
 namespace ztvm {
 
-constexpr int kGemmStages = 3;       // activation / dequantised-weight ring
-constexpr int kGemmWStages = 3;      // packed-weight ring (each slot holds four k blocks)
+constexpr int kGemmStages = 4;       // activation / dequantised-weight ring
+constexpr int kGemmWStages = 2;      // packed-weight ring (each slot holds four k blocks)
 constexpr int kGemmWChunk = 4;       // k blocks per packed-weight slot: 32 words = 128 bytes per row
 constexpr int kGemmDqWarps = 8;      // dequantiser warps (two per SM sub-partition)
 constexpr int kGemmThreads = 96 + kGemmDqWarps * 32;   // two TMA warps + MMA warp + dequantisers
@@ -79,7 +79,7 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kGemmStages; ++s) {
-      mbar_init(bar_full(s), 1 + kGemmDqWarps * 32);   // the TMA producer's arrival (with the byte count) + every dequantiser thread
+      mbar_init(bar_full(s), 1 + kGemmDqWarps * 32 / 2);   // the TMA producer's arrival (with the byte count) + every thread of one dequantiser group
       mbar_init(bar_empty(s), 1);
     }
     for (int s = 0; s < kGemmWStages; ++s) {
@@ -180,13 +180,19 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
     }
   } else {
     // ================= dequantisers (warps 3..10), then epilogue =================
+    // The dequantisers work as two groups of four warps that take alternate k blocks. One k block is a chain of waits,
+    // shared loads, conversions and stores whose latency, not its instruction count, set the pace when every thread
+    // worked on every k block; two groups keep two k blocks in flight.
     const int t = threadIdx.x - 96;                  // 0..255
-    constexpr int TPR = (kGemmDqWarps * 32) / BN;    // threads per weight row (BN = 128 -> 2, 64 -> 4, 256 -> 1)
-    constexpr int WPT = (kGemmBK / 8) / TPR;         // 8-code words per thread per k block (4, 2, 8)
+    constexpr int kDqGroups = 2;
+    constexpr int GT = kGemmDqWarps * 32 / kDqGroups;   // threads per group
+    constexpr int TPR = GT / BN;                     // threads per weight row (BN = 128 -> 1, 64 -> 2)
+    constexpr int WPT = (kGemmBK / 8) / TPR;         // 8-code words per thread per k block (8, 4)
     static_assert(TPR >= 1 && WPT >= 2 && TPR * WPT == 8, "unsupported BN");
+    const int grp = t / GT, tg = t % GT;
     const int gshift = (int)p.group_shift;
-    const uint32_t r_tile = (uint32_t)(t / TPR);     // weight row within the tile
-    const uint32_t part = (uint32_t)(t % TPR);       // which run of WPT words of the 8-word k block
+    const uint32_t r_tile = (uint32_t)(tg / TPR);    // weight row within the tile
+    const uint32_t part = (uint32_t)(tg % TPR);      // which run of WPT words of the 8-word k block
     const uint32_t row = min(n0 + r_tile, p.N - 1);
     const unsigned short* srow = reinterpret_cast<const unsigned short*>(p.S) + (size_t)row * p.SPR;
     const unsigned short* brow = reinterpret_cast<const unsigned short*>(p.B) + (size_t)row * p.SPR;
@@ -216,13 +222,14 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
       for (int i = 0; i < kUnroll; ++i) {
         const uint32_t kb = kb0 + i;
         if (kb >= num_kb || !ok) break;
+        if ((i & 1) != grp) continue;                     // the other group's k block
         const int s = (int)(kb % kGemmStages);
         const uint32_t ph = (kb / kGemmStages) & 1u;
         const uint32_t c = kb / kGemmWChunk;              // packed-weight chunk and slot
         const int ws = (int)(c % kGemmWStages);
         constexpr int kJ = kGemmWChunk;
         const int j = i % kJ;                             // k block inside the chunk (kb0 is a multiple of 8)
-        if (j == 0) ok = mbar_wait(bar_w_full(ws), (c / kGemmWStages) & 1u, p.status, 7u, abort_flag);
+        if (j == grp) ok = mbar_wait(bar_w_full(ws), (c / kGemmWStages) & 1u, p.status, 7u, abort_flag);   // this group's first k block of the chunk
         // codes of this k block: words [j*8 + part*WPT, +WPT) of the row's 32-word line
         uint32_t wv[WPT];
         if (ok) {
@@ -271,7 +278,7 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
         }
         // Last read of the packed slot: it goes back to the producer only after the stores that consume its words.
         // (A release straight after the loads let the refill land before the loads had been performed.)
-        if (j == kJ - 1 || kb + 1 == num_kb) {
+        if (j + kDqGroups >= kJ || kb + kDqGroups >= num_kb) {   // this group's last k block of the chunk
           __syncwarp();
           if (lane == 0) mbar_arrive(bar_w_empty(ws));
         }
