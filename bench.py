@@ -314,6 +314,45 @@ def run_sharded(args, rank, world, local):
         dist.destroy_process_group()
 
 
+def quick_device_rate(ctx, torch, device, z, workload, steps, warmup, seed=4321):
+    """Device-timed rate of another workload, same method as the main one (rotating sets >= 4x L2, CUDA-graph replay,
+    CUDA events on the launching stream): the decode half of the metric, reported beside the prefill GEMM."""
+    shapes = workload_shapes(workload)
+    sets, R = make_sets(shapes, seed, torch, device)
+    xs = [torch.randn((M, K), device=device).to(torch.float16) for _, N, K, M, _ in shapes]
+    descs = [z.MmDesc(K, N, M, 64, 4, 1, int(f32)) for _, N, K, M, f32 in shapes]
+    stream = torch.cuda.Stream(device)
+
+    def one_pass():
+        for one in sets:
+            for (W, s, b, y), x, d in zip(one, xs, descs):
+                ctx.int4_matmul(d, y, x, s, W, b, stream)
+
+    with torch.cuda.stream(stream):
+        one_pass()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            one_pass()
+        for _ in range(warmup):
+            graph.replay()
+        stream.synchronize()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record(stream)
+        for _ in range(steps):
+            graph.replay()
+        ev1.record(stream)
+        stream.synchronize()
+    ms = ev0.elapsed_time(ev1) / steps
+    nbytes = R * sum(algorithmic_bytes(N, K, M, out_bytes=4 if f32 else 2) for _, N, K, M, f32 in shapes)
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    peak = measured_peaks()["hbm"]
+    del sets, graph
+    torch.cuda.empty_cache()
+    return {"workload": workload, "value": gbs, "unit": "GB/s", "frac": gbs / peak, "peak": peak,
+            "avg_launch_us": ms * 1e3 / (R * len(shapes)), "launches": int(steps * R * len(shapes))}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -322,6 +361,7 @@ def main():
     ap.add_argument("--workload", default="prefill_gemm_m512")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-decode", action="store_true", help="default workload: skip the M = 1 rates reported beside it")
     ap.add_argument("--m-rows", type=int, default=1, help="activation rows of layer_set_nshard")
     ap.add_argument("--tokens", type=int, default=2048, help="tokens of moe_ep: per rank (weak) or whole job (strong)")
     ap.add_argument("--ep-scaling", default="weak", choices=["weak", "strong"])
@@ -458,6 +498,14 @@ def main():
            "d2h_bytes_per_step": R * M * N * (4 if f32 else 2),
            "what": "ztvm_int4_matmul_host per launch: pinned x -> device, kernel, y -> host, sync; weights resident"}
 
+    # ---- the decode half of the metric (M = 1, GB/s against the measured copy bandwidth), rank 0 of the default run ----
+    decode = None
+    if args.workload == "prefill_gemm_m512" and rank == 0 and not args.no_decode:
+        del sets, graph, e2e_sets
+        torch.cuda.empty_cache()
+        decode = [quick_device_rate(ctx, torch, device, z, w, max(3, args.steps // 2), args.warmup)
+                  for w in ("decode_gemv", "decode_layer_set", "shape:151936x4096x1xf32")]
+
     out = {
         "metric": METRIC, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -468,6 +516,7 @@ def main():
                    "parallelism": "replicas" if world > 1 else "single"},
         "roofline": roof, "e2e": e2e, "gpu_launches": int(args.steps * n_launch_step),
         "clocks": clocks.summary(), "verified": verified,
+        "decode": decode,
     }
     if rank == 0:
         if not args.no_cpu_baseline:
