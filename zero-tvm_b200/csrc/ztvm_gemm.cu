@@ -77,6 +77,7 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
   const uint32_t num_kb = p.K / kGemmBK;
   constexpr uint32_t kTmemCols = (MB * BN) <= 32 ? 32 : (MB * BN) <= 64 ? 64 : (MB * BN) <= 128 ? 128 : (MB * BN) <= 256 ? 256 : 512;
 
+  if (threadIdx.x == 32) { tma_prefetch_desc(&tmap_x); tma_prefetch_desc(&tmap_w); tma_prefetch_desc(&tmap_y); }
   if (threadIdx.x == 0) {
     for (int s = 0; s < kGemmStages; ++s) {
       mbar_init(bar_full(s), 1 + kGemmDqWarps * 32 / 2);   // the TMA producer's arrival (with the byte count) + every thread of one dequantiser group
