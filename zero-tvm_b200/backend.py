@@ -188,7 +188,11 @@ class CudaMatmulBackend:
 
     def dispatch(self, entry: str, bindings: Sequence, grid: Sequence[int] = (1, 1, 1), stream=None):
         """bindings = [out, in, scales, weights, PODArgs, biases?, ids?] in bind-group slot order;
-        PODArgs is the list of u32 the engine writes into the uniform buffer."""
+        PODArgs is the list of u32 the engine writes into the uniform buffer.
+
+        stream=None launches on the context's own stream, which is non-blocking: work queued on another stream (a
+        tensor library's fills and copies, say) is NOT ordered against it. Pass that library's stream (a handle, a
+        torch.cuda.Stream, or 1 for the legacy default stream), or synchronise both sides around the call."""
         info = parse_entry(entry)
         if len(bindings) < 5:
             raise ValueError("bind group needs [out, in, scales, weights, PODArgs, ...]")
