@@ -252,6 +252,16 @@ def test_host_buffer_entry_point(backend, dev, oracle_c):
     backend.ctx.int4_matmul_host(d, y, np.ascontiguousarray(p["x"]), dev.put(p["scales"]), dev.put(p["W"]),
                                  dev.put(p["biases"]))
     check_y(y, p, oracle_c)
+    # page-locked caller buffers take the direct DMA path (no staging copy): same bits; mixed pinned / pageable too
+    import torch
+    xp = torch.from_numpy(np.ascontiguousarray(p["x"])).pin_memory()
+    yp = torch.zeros((4, 1024), dtype=torch.float16).pin_memory()
+    W, s_, b = dev.put(p["W"]), dev.put(p["scales"]), dev.put(p["biases"])
+    backend.ctx.int4_matmul_host(d, yp, xp, s_, W, b)
+    assert np.array_equal(yp.numpy().view(np.uint16), y.view(np.uint16))
+    y2 = np.zeros((4, 1024), dtype=np.float16)
+    backend.ctx.int4_matmul_host(d, y2, xp, s_, W, b)
+    assert np.array_equal(y2.view(np.uint16), y.view(np.uint16))
 
 
 def test_multi_destination_matmul_matches_the_single_destination_call(backend, dev, oracle_c):

@@ -62,6 +62,16 @@ ztvm_status check_ctx(ztvm_ctx* ctx) {
   return ZTVM_OK;
 }
 
+// True when `p` is page-locked host memory known to the runtime (cudaHostAlloc / cudaHostRegister).
+bool host_is_pinned(const void* p) {
+  cudaPointerAttributes a;
+  if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+    cudaGetLastError();   // older runtimes report plain malloc memory as an error: clear it
+    return false;
+  }
+  return a.type == cudaMemoryTypeHost;
+}
+
 bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
 int log2_exact(uint32_t v) {
@@ -279,16 +289,22 @@ ztvm_status ztvm_int4_matmul_host(ztvm_ctx* ctx, const ztvm_mm_desc* d, void* y_
   if ((s = check_desc(d, true))) return s;
   if (!y_host || !x_host) return fail(ZTVM_ERR_NULL_POINTER, "y_host/x_host must be non-NULL");
   const size_t xb = (size_t)d->M * d->K * 2, yb = (size_t)d->M * d->N * (d->out_f32 ? 4 : 2);
-  if ((s = grow(&ctx->h_pinned, &ctx->h_pinned_bytes, xb + yb, true))) return s;
+  // Page-locked caller buffers are copied by the DMA engines directly; pageable ones go through the context's
+  // pinned staging buffer (an extra host memcpy each way).
+  const bool x_pinned = host_is_pinned(x_host), y_pinned = host_is_pinned(y_host);
+  const size_t stage = (x_pinned ? 0 : xb) + (y_pinned ? 0 : yb);
+  if (stage && (s = grow(&ctx->h_pinned, &ctx->h_pinned_bytes, stage, true))) return s;
   if ((s = grow(&ctx->d_x, &ctx->d_x_bytes, xb, false))) return s;
   if ((s = grow(&ctx->d_y, &ctx->d_y_bytes, yb, false))) return s;
   char* hp = static_cast<char*>(ctx->h_pinned);
-  memcpy(hp, x_host, xb);
-  ZTVM_CUDA(cudaMemcpyAsync(ctx->d_x, hp, xb, cudaMemcpyHostToDevice, ctx->stream));
+  const void* x_src = x_host;
+  if (!x_pinned) { memcpy(hp, x_host, xb); x_src = hp; }
+  void* y_dst = y_pinned ? y_host : static_cast<void*>(hp + (x_pinned ? 0 : xb));
+  ZTVM_CUDA(cudaMemcpyAsync(ctx->d_x, x_src, xb, cudaMemcpyHostToDevice, ctx->stream));
   if ((s = ztvm_int4_matmul(ctx, d, ctx->d_y, ctx->d_x, scales, packed_w, biases, ctx->stream))) return s;
-  ZTVM_CUDA(cudaMemcpyAsync(hp + xb, ctx->d_y, yb, cudaMemcpyDeviceToHost, ctx->stream));
+  ZTVM_CUDA(cudaMemcpyAsync(y_dst, ctx->d_y, yb, cudaMemcpyDeviceToHost, ctx->stream));
   ZTVM_CUDA(cudaStreamSynchronize(ctx->stream));
-  memcpy(y_host, hp + xb, yb);
+  if (!y_pinned) memcpy(y_host, y_dst, yb);
   return ZTVM_OK;
 }
 
