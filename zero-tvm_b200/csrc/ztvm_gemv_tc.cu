@@ -26,7 +26,7 @@ namespace ztvm {
 
 constexpr uint32_t kTcMaxAccBytes = 32 * 1024;       // cross-K-tile accumulators (only when K > 4096)
 // rounds between two meetings: the partial buffers hold 2 x warps x rounds x 16 rows x NT floats
-__host__ __device__ constexpr int tc_rounds(int nt) { return nt <= 2 ? 4 : 2; }
+__host__ __device__ constexpr int tc_rounds(int nt) { return nt <= 4 ? 4 : 2; }
 
 
 // NT = tokens padded to a power of two. The eight columns of an MMA are (group, token) pairs: with NT tokens one
