@@ -138,7 +138,7 @@ def make_sets(shapes, seed, torch, device):
     return sets, R
 
 
-def cpu_baseline(shapes, budget_s=12.0):
+def cpu_baseline(shapes, limit_s=12.0):
     """The oracle's reference-order CPU matmul (C, OpenMP, all host threads) on a bounded sample."""
     import zero_tvm_b200 as z
     from oracle import ztvm_oracle_c as zc
@@ -152,7 +152,7 @@ def cpu_baseline(shapes, budget_s=12.0):
         zc.gemv_ref(p["x"], p["W"], p["scales"], p["biases"], 64, out_f32=f32)
         n += 1
         dt = time.perf_counter() - t0
-        if dt > budget_s or n >= 50:
+        if dt > limit_s or n >= 50:
             break
     per = dt / n
     return dict(seconds_per_sample=per, rows=Ms, N=N, K=K, cores=zc.num_threads(),
@@ -168,7 +168,7 @@ def run_reference_arm(args, rank):
     is_gemm = shapes[0][3] > 8
     vals = []
     for _ in range(max(1, args.steps)):
-        cb = cpu_baseline(shapes, budget_s=max(2.0, 20.0 / max(1, args.steps)))
+        cb = cpu_baseline(shapes, limit_s=max(2.0, 20.0 / max(1, args.steps)))
         label, N, K, M, f32 = shapes[0]
         if is_gemm:
             vals.append(2.0 * cb["rows"] * N * K / cb["seconds_per_sample"] / 1e12)

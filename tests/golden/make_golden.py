@@ -31,7 +31,9 @@ def load_dequant_from(ref_root: str):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <path to a checkout of the reference project>")
+    ref_root = sys.argv[1]
     dequant_from = load_dequant_from(ref_root)
     cases = {
         # name: (N, K, seed, scale sigma, extreme)

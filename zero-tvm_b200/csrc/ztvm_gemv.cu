@@ -616,7 +616,7 @@ cudaError_t launch_gemv(GemvParams p, int bits, bool moe, uint32_t tokens, uint3
   int rows = 4;
   while (rows > 1 && ((uint64_t)(p.N + kGemvWarps * rows - 1) / (kGemvWarps * rows)) * pairs < (uint64_t)sm_count * 4)
     rows >>= 1;
-  if (mt == 8 && rows > 2) rows = 2;  // register budget
+  if (mt == 8 && rows > 2) rows = 2;  // register pressure
   const uint32_t units = p.K >> 5;
   uint32_t tile_units = (uint32_t)(kGemvTileElems / mt) >> 5;
   const uint32_t units_up = (units + 31) & ~31u;
