@@ -18,6 +18,8 @@
 //     into the f32 accumulators with round-to-nearest FMAs:  acc += s*2^24*lo + s*2^20*hi + b*sum(x).
 //   * every kTcRounds rounds the K-slice partials of the warps meet in shared memory (double-buffered, one
 //     __syncthreads per meeting, fixed summation order: results are deterministic).
+#include <cstdlib>
+
 #include "ztvm_device.cuh"
 #include "ztvm_kernels.h"
 #include "ztvm_stream_mma.cuh"
@@ -318,7 +320,8 @@ static cudaError_t launch_tc_one(const GemvParams& p, unsigned grid, size_t smem
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  static const bool no_pdl = [] { const char* e = getenv("ZTVM_NO_PDL"); return e && e[0] == '1'; }();   // measurement knob
+  cfg.numAttrs = no_pdl ? 0 : 1;
   return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
