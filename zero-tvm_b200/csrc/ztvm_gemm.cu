@@ -78,18 +78,36 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
   constexpr uint32_t kTmemCols = (MB * BN) <= 32 ? 32 : (MB * BN) <= 64 ? 64 : (MB * BN) <= 128 ? 128 : (MB * BN) <= 256 ? 256 : 512;
 
   if (threadIdx.x == 32) { tma_prefetch_desc(&tmap_x); tma_prefetch_desc(&tmap_w); tma_prefetch_desc(&tmap_y); }
+  // Each TMA producer initialises the barriers its own copies signal and starts its first loads right away: they
+  // fly while the other warps allocate tensor memory and meet at the block barrier below. Everyone else touches
+  // those barriers only after that barrier.
   if (threadIdx.x == 0) {
     for (int s = 0; s < kGemmStages; ++s) {
       mbar_init(bar_full(s), 1 + kGemmDqWarps * 32 / 2);   // the TMA producer's arrival (with the byte count) + every thread of one dequantiser group
       mbar_init(bar_empty(s), 1);
     }
+    mbar_init(bar_accum, 1);
+    *abort_flag = 0u;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    for (uint32_t kb = 0; kb < (uint32_t)kGemmStages && kb < num_kb; ++kb) {
+      mbar_arrive_expect_tx(bar_full((int)kb), (uint32_t)L::kABytes);
+#pragma unroll
+      for (int mb = 0; mb < MB; ++mb)
+        tma_load_2d(a_ring + kb * L::kABytes + mb * (128 * kGemmBK * 2), &tmap_x, bar_full((int)kb), (int)(kb * kGemmBK),
+                    (int)(m0 + mb * 128));
+    }
+  }
+  if (threadIdx.x == 64) {
     for (int s = 0; s < kGemmWStages; ++s) {
       mbar_init(bar_w_full(s), 1);
       mbar_init(bar_w_empty(s), kGemmDqWarps);
     }
-    mbar_init(bar_accum, 1);
-    *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    const uint32_t num_chunks0 = (num_kb + kGemmWChunk - 1) / kGemmWChunk;
+    for (uint32_t c = 0; c < (uint32_t)kGemmWStages && c < num_chunks0; ++c) {
+      mbar_arrive_expect_tx(bar_w_full((int)c), (uint32_t)L::kWBytes);
+      tma_load_2d(w_ring + c * L::kWBytes, &tmap_w, bar_w_full((int)c), (int)(c * 32), (int)n0);
+    }
   }
   if (warp == 1) {  // the MMA warp owns the TMEM allocation
     tmem_alloc(smem_u32(tmem_slot), kTmemCols);
@@ -103,8 +121,8 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
   if (warp == 0) {
     // ================= TMA producer =================
     if (lane == 0) {
-      uint32_t issued = 0;
-      for (uint32_t kb = 0; kb < num_kb; ++kb) {
+      uint32_t issued = num_kb < (uint32_t)kGemmStages ? num_kb : (uint32_t)kGemmStages;   // the first stages went out before the block barrier
+      for (uint32_t kb = issued; kb < num_kb; ++kb) {
         const int s = kb % kGemmStages;
         const uint32_t ph = (kb / kGemmStages) & 1u;
         if (kb >= kGemmStages && !mbar_wait(bar_empty(s), ph ^ 1u, p.status, 1u, abort_flag)) break;
@@ -161,8 +179,8 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
     // ================= TMA producer: packed weights =================
     if (lane == 0) {
       const uint32_t num_chunks = (num_kb + kGemmWChunk - 1) / kGemmWChunk;
-      uint32_t issued = 0;
-      for (uint32_t c = 0; c < num_chunks; ++c) {
+      uint32_t issued = num_chunks < (uint32_t)kGemmWStages ? num_chunks : (uint32_t)kGemmWStages;   // sent before the block barrier
+      for (uint32_t c = issued; c < num_chunks; ++c) {
         const int s = c % kGemmWStages;
         const uint32_t ph = (c / kGemmWStages) & 1u;
         if (c >= kGemmWStages && !mbar_wait(bar_w_empty(s), ph ^ 1u, p.status, 6u, abort_flag)) break;
