@@ -30,6 +30,7 @@ struct ztvm_ctx {
   // env ZTVM_MOE_GROUPED (a measurement knob): 0 forces the per-pair GEMV, 1 the tensor-core tiles, 2 the streaming
   // grouped kernel; unset = by size (below 128 pairs per-pair; then streaming while an expert sees few pairs)
   int moe_grouped;
+  int gemm_sm;      // env ZTVM_GEMM=sm: the GEMM with both operands in shared memory (a measurement knob)
 };
 
 namespace {
@@ -194,6 +195,8 @@ ztvm_status ztvm_init(int32_t device_ordinal, ztvm_ctx** out_ctx) {
   }
   const char* ng = getenv("ZTVM_NO_GEMM");
   c->no_gemm = (ng && ng[0] == '1') ? 1 : 0;
+  const char* gk = getenv("ZTVM_GEMM");
+  c->gemm_sm = (gk && !strcmp(gk, "sm")) ? 1 : 0;
   const char* mg = getenv("ZTVM_MOE_GROUPED");
   c->moe_grouped = !mg ? -1 : (mg[0] == '1' ? 1 : mg[0] == '2' ? 2 : 0);
   const char* gp = getenv("ZTVM_GEMV_PATH");
@@ -234,10 +237,12 @@ ztvm_status ztvm_int4_matmul(ztvm_ctx* ctx, const ztvm_mm_desc* d, void* y, cons
   cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : ctx->stream;
   if (d->M > 8 && ztvm::gemm_w4_supported((int)d->bits, d->group, d->K) && !ctx->no_gemm) {
     if (!aligned(y, 16)) return fail(ZTVM_ERR_ALIGNMENT, "y must be 16-byte aligned for the GEMM path");
-    ZTVM_CUDA(ztvm::launch_gemm_w4(static_cast<const uint32_t*>(packed_w), static_cast<const __half*>(scales),
-                                   d->affine ? static_cast<const __half*>(biases) : nullptr,
-                                   static_cast<const __half*>(x), y, d->M, d->N, d->K, (uint32_t)log2_exact(d->group),
-                                   d->out_f32 != 0, ctx->err_counter + 1, st));
+    // M > 128: weights as the A operand in tensor memory (256 tokens per instruction); up to 128 rows the tiles with
+    // both operands in shared memory, whose 64-row weight tiles give twice as many CTAs
+    auto launch = (ctx->gemm_sm || d->M <= 128) ? ztvm::launch_gemm_w4 : ztvm::launch_gemm_w4_ta;
+    ZTVM_CUDA(launch(static_cast<const uint32_t*>(packed_w), static_cast<const __half*>(scales),
+                     d->affine ? static_cast<const __half*>(biases) : nullptr, static_cast<const __half*>(x), y, d->M, d->N,
+                     d->K, (uint32_t)log2_exact(d->group), d->out_f32 != 0, ctx->err_counter + 1, st));
     return ZTVM_OK;
   }
   // Otherwise rows are processed in slabs of at most 8 by the GEMV.

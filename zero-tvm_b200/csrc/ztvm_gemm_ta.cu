@@ -1,0 +1,368 @@
+// Prefill GEMM, M > 8, 4-bit weights: y[M, N] = x[M, K] * W16[N, K]^T on tcgen05 with the DEQUANTISED WEIGHTS AS THE
+// A OPERAND IN TENSOR MEMORY (replaces the matrix-unit GEMMs of int4_matmul.gen.ts:1058-1456; contract of
+// ztvm_int4_matmul for M > 8).
+//
+// Why this orientation. With both operands in shared memory a 128 x 128 x 16 tcgen05.mma reads 8 KB per ~68 cycles,
+// close to the shared-memory port's whole rate, next to the dequantisers' stores and the TMA writes (ztvm_gemm.cu).
+// Here the weights take the M side of the MMA (128 weight rows = 128 TMEM
+// lanes) and go from the dequantisers' registers straight into tensor memory with tcgen05.st; the activations take
+// the N side (256 tokens per instruction) and are the only operand read from shared memory: 32 KB per k block
+// instead of 64 + 16. D is [weight row][token] in tensor memory; the epilogue writes it transposed (a warp's 32 lanes
+// are 32 consecutive output columns of one token: 64-byte stores).
+//
+// Roles (352 threads): warp 0 TMA-loads activation tiles (NT tokens x 64 k, 128-byte swizzle); warp 2 TMA-loads
+// packed weight tiles (128 rows x 32 words = four k blocks); warps 3..10 dequantise: warp w may touch TMEM lanes
+// 32 (w % 4) .. +31, so it owns those 32 weight rows, and the two warps that share a lane quarter split the k block
+// in halves (16 TMEM columns each); warp 1 allocates tensor memory and issues the MMAs. Every wait is bounded
+// (status word, as in ztvm_gemm.cu).
+#include "ztvm_kernels.h"
+#include "ztvm_tc.cuh"
+
+namespace ztvm {
+
+constexpr int kTaStages = 4;        // activation tiles in shared memory and weight slices in tensor memory
+constexpr int kTaWStages = 2;       // packed-weight ring (each slot holds four k blocks)
+constexpr int kTaWChunk = 4;
+constexpr int kTaDqWarps = 8;
+constexpr int kTaThreads = 96 + kTaDqWarps * 32;
+constexpr int kTaRows = 128;        // weight rows per CTA = TMEM lanes
+
+struct GemmTaParams {
+  const __half* S;
+  const __half* B;   // nullptr: symmetric
+  void* Y;
+  uint32_t M, N, K, SPR, group_shift, out_f32;
+  uint32_t* status;
+};
+
+template <int NT>
+struct GemmTaSmem {
+  static constexpr int kXBytes = NT * kGemmBK * 2;            // per stage
+  static constexpr int kWBytes = kTaRows * 128;               // per packed-weight slot
+  static constexpr int kOffW = kTaStages * kXBytes;
+  static constexpr int kOffBar = kOffW + kTaWStages * kWBytes;
+  static constexpr int kTotal = kOffBar + 256;
+};
+
+__device__ __forceinline__ void umma_f16_ta(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+        "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+template <int NT, bool AFFINE>
+__global__ void __launch_bounds__(kTaThreads, 1)
+gemm_w4_ta_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+                  const GemmTaParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  using L = GemmTaSmem<NT>;
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t x_ring = base, w_ring = base + L::kOffW, bars = base + L::kOffBar;
+  auto bar_full = [&](int s) { return bars + 8u * s; };
+  auto bar_empty = [&](int s) { return bars + 8u * (kTaStages + s); };
+  auto bar_w_full = [&](int s) { return bars + 8u * (2 * kTaStages + s); };
+  auto bar_w_empty = [&](int s) { return bars + 8u * (2 * kTaStages + kTaWStages + s); };
+  constexpr int kNumBars = 2 * kTaStages + 2 * kTaWStages + 1;
+  const uint32_t bar_accum = bars + 8u * (kNumBars - 1);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + L::kOffBar + 8 * kNumBars);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t n0 = blockIdx.x * kTaRows;
+  const uint32_t m0 = blockIdx.y * NT;
+  const uint32_t num_kb = p.K / kGemmBK;
+  constexpr uint32_t kColA = NT;                                 // weight slices start after the accumulator columns
+  constexpr uint32_t kTmemCols = NT + kTaStages * 32 <= 256 ? 256 : 512;
+
+  if (threadIdx.x == 32) { tma_prefetch_desc(&tmap_x); tma_prefetch_desc(&tmap_w); }
+  // Each TMA producer initialises the barriers its own copies signal and starts its first loads before the block
+  // barrier: they fly while tensor memory is allocated.
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kTaStages; ++s) {
+      mbar_init(bar_full(s), 1 + kTaDqWarps * 32);   // the activation tile (with its byte count) + every dequantiser thread
+      mbar_init(bar_empty(s), 1);
+    }
+    mbar_init(bar_accum, 1);
+    *abort_flag = 0u;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    for (uint32_t kb = 0; kb < (uint32_t)kTaStages && kb < num_kb; ++kb) {
+      mbar_arrive_expect_tx(bar_full((int)kb), (uint32_t)L::kXBytes);
+#pragma unroll
+      for (int b = 0; b < NT / 128; ++b)
+        tma_load_2d(x_ring + kb * L::kXBytes + b * (128 * kGemmBK * 2), &tmap_x, bar_full((int)kb), (int)(kb * kGemmBK), (int)(m0 + b * 128));
+    }
+  }
+  if (threadIdx.x == 64) {
+    for (int s = 0; s < kTaWStages; ++s) {
+      mbar_init(bar_w_full(s), 1);
+      mbar_init(bar_w_empty(s), kTaDqWarps);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    const uint32_t nc = (num_kb + kTaWChunk - 1) / kTaWChunk;
+    for (uint32_t c = 0; c < (uint32_t)kTaWStages && c < nc; ++c) {
+      mbar_arrive_expect_tx(bar_w_full((int)c), (uint32_t)L::kWBytes);
+      tma_load_2d(w_ring + c * L::kWBytes, &tmap_w, bar_w_full((int)c), (int)(c * 32), (int)n0);
+    }
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ================= TMA producer: activations =================
+    if (lane == 0) {
+      uint32_t issued = num_kb < (uint32_t)kTaStages ? num_kb : (uint32_t)kTaStages;
+      for (uint32_t kb = issued; kb < num_kb; ++kb) {
+        const int s = kb % kTaStages;
+        const uint32_t ph = (kb / kTaStages) & 1u;
+        if (!mbar_wait(bar_empty(s), ph ^ 1u, p.status, 1u, abort_flag)) break;
+        mbar_arrive_expect_tx(bar_full(s), (uint32_t)L::kXBytes);
+#pragma unroll
+        for (int b = 0; b < NT / 128; ++b)
+          tma_load_2d(x_ring + s * L::kXBytes + b * (128 * kGemmBK * 2), &tmap_x, bar_full(s), (int)(kb * kGemmBK), (int)(m0 + b * 128));
+        issued = kb + 1;
+      }
+      if (*abort_flag) {   // the consumer stopped: wait (bounded) until the copies already issued have landed
+        const uint32_t first = issued > (uint32_t)kTaStages ? issued - kTaStages : 0u;
+        for (uint32_t kb = first; kb < issued; ++kb) {
+          const long long t0 = clock64();
+          while (!mbar_try_wait(bar_full(kb % kTaStages), (kb / kTaStages) & 1u) &&
+                 (unsigned long long)(clock64() - t0) < kWaitCycles) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ================= MMA issuer =================
+    if (lane == 0) {
+      constexpr uint32_t idesc = idesc_f16(NT);
+      const uint64_t b0 = smem_desc_sw128(x_ring);
+      uint32_t s = 0, ph = 0;
+      bool ok = true;
+      for (uint32_t kb = 0; kb < num_kb; ++kb) {
+        ok = mbar_wait(bar_full(s), ph, p.status, 2u, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const uint64_t bdesc = b0 + (uint64_t)(s * (L::kXBytes >> 4));
+        const uint32_t a_tmem = tmem_base + kColA + s * 32u;
+#pragma unroll
+        for (int k = 0; k < kGemmBK / 16; ++k)   // 16 k elements: 8 TMEM columns of A, 32 bytes along the swizzled B row
+          umma_f16_ta(tmem_base, a_tmem + (uint32_t)(8 * k), bdesc + (uint64_t)(2 * k), idesc, (kb | (uint32_t)k) ? 1u : 0u);
+        umma_commit(bar_empty(s));   // the activation tile and the weight slice are free once these MMAs have read them
+        if (++s == (uint32_t)kTaStages) { s = 0; ph ^= 1u; }
+      }
+      if (ok) umma_commit(bar_accum);
+    }
+  } else if (warp == 2) {
+    // ================= TMA producer: packed weights =================
+    if (lane == 0) {
+      const uint32_t num_chunks = (num_kb + kTaWChunk - 1) / kTaWChunk;
+      uint32_t issued = num_chunks < (uint32_t)kTaWStages ? num_chunks : (uint32_t)kTaWStages;
+      for (uint32_t c = issued; c < num_chunks; ++c) {
+        const int s = c % kTaWStages;
+        const uint32_t ph = (c / kTaWStages) & 1u;
+        if (!mbar_wait(bar_w_empty(s), ph ^ 1u, p.status, 6u, abort_flag)) break;
+        mbar_arrive_expect_tx(bar_w_full(s), (uint32_t)L::kWBytes);
+        tma_load_2d(w_ring + s * L::kWBytes, &tmap_w, bar_w_full(s), (int)(c * 32), (int)n0);
+        issued = c + 1;
+      }
+      if (*abort_flag) {
+        const uint32_t first = issued > (uint32_t)kTaWStages ? issued - kTaWStages : 0u;
+        for (uint32_t c = first; c < issued; ++c) {
+          const long long t0 = clock64();
+          while (!mbar_try_wait(bar_w_full(c % kTaWStages), (c / kTaWStages) & 1u) &&
+                 (unsigned long long)(clock64() - t0) < kWaitCycles) {}
+        }
+      }
+    }
+  } else {
+    // ================= dequantisers (warps 3..10), then epilogue =================
+    const int quarter = warp & 3;                       // TMEM lanes this warp may touch: [32 * quarter, +32)
+    const uint32_t part = (uint32_t)(warp - 3) >> 2;    // which half of the k block (the two warps of a quarter)
+    const uint32_t r_tile = (uint32_t)(quarter * 32 + lane);
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const int gshift = (int)p.group_shift;
+    const uint32_t row = min(n0 + r_tile, p.N - 1);
+    const unsigned short* srow = reinterpret_cast<const unsigned short*>(p.S) + (size_t)row * p.SPR;
+    const unsigned short* brow = reinterpret_cast<const unsigned short*>(p.B) + (size_t)row * p.SPR;
+    bool ok = true;
+    // group 64: eight groups per 16-byte load, fetched eight k blocks ahead; scalar loads otherwise
+    const bool vec_sb = gshift == 6 && (p.SPR % 8u) == 0 && ((reinterpret_cast<uintptr_t>(p.S) | reinterpret_cast<uintptr_t>(p.B)) & 15u) == 0;
+    uint4 sv_cur = make_uint4(0, 0, 0, 0), bv_cur = sv_cur, sv_nxt = sv_cur, bv_nxt = sv_cur;
+    auto load_sb8 = [&](uint4& sv, uint4& bv, uint32_t kb8) {
+      if (kb8 >= num_kb) return;
+      sv = __ldg(reinterpret_cast<const uint4*>(srow + kb8));
+      if (AFFINE) bv = __ldg(reinterpret_cast<const uint4*>(brow + kb8));
+    };
+    auto pick16 = [](const uint4& v, int i) -> unsigned short {
+      const uint32_t wsel = (i >> 1) == 0 ? v.x : (i >> 1) == 1 ? v.y : (i >> 1) == 2 ? v.z : v.w;
+      return (unsigned short)((i & 1) ? (wsel >> 16) : (wsel & 0xFFFFu));
+    };
+    if (vec_sb) { load_sb8(sv_cur, bv_cur, 0); load_sb8(sv_nxt, bv_nxt, 8); }
+
+    const uint8_t* const wrow_sm = gen_base + L::kOffW + (r_tile >> 3) * 1024 + (r_tile & 7) * 128;
+    constexpr int kUnroll = 8;
+    for (uint32_t kb0 = 0; kb0 < num_kb && ok; kb0 += kUnroll) {
+#pragma unroll
+      for (int i = 0; i < kUnroll; ++i) {
+        const uint32_t kb = kb0 + i;
+        if (kb >= num_kb || !ok) break;
+        const int s = (int)(kb % kTaStages);
+        const uint32_t ph = (kb / kTaStages) & 1u;
+        const uint32_t c = kb / kTaWChunk;
+        const int ws = (int)(c % kTaWStages);
+        const int j = i % kTaWChunk;
+        if (j == 0) ok = mbar_wait(bar_w_full(ws), (c / kTaWStages) & 1u, p.status, 7u, abort_flag);
+        uint4 wv = make_uint4(0, 0, 0, 0);
+        if (ok) wv = *reinterpret_cast<const uint4*>(wrow_sm + ws * L::kWBytes + ((((uint32_t)j * 2 + part) ^ (r_tile & 7)) << 4));
+        // the TMEM slice of stage s was last read by the MMAs of k block kb - kTaStages
+        if (ok && kb >= (uint32_t)kTaStages) {
+          ok = mbar_wait(bar_empty(s), ph ^ 1u, p.status, 4u, abort_flag);
+          tc_fence_after();
+        }
+        if (ok) {
+          unsigned short s16, b16 = 0;
+          if (vec_sb) {
+            s16 = pick16(sv_cur, i);
+            if (AFFINE) b16 = pick16(bv_cur, i);
+          } else {
+            const uint32_t g = (kb * kGemmBK + part * 32) >> gshift;
+            s16 = __ldg(srow + g);
+            if (AFFINE) b16 = __ldg(brow + g);
+          }
+          const float sf = __half2float(__ushort_as_half(s16)), bf = __half2float(__ushort_as_half(b16));
+          const uint32_t words[4] = {wv.x, wv.y, wv.z, wv.w};
+          uint32_t a[16];
+#pragma unroll
+          for (int wi = 0; wi < 4; ++wi) {
+            const uint4 v = dequant_word_w16<AFFINE>(words[wi], s16, sf, bf);
+            a[4 * wi] = v.x; a[4 * wi + 1] = v.y; a[4 * wi + 2] = v.z; a[4 * wi + 3] = v.w;
+          }
+          // 32 weights of this row = 16 TMEM columns (two k-adjacent f16 per column) of this thread's lane
+          tmem_st16(tmem_base + lane_base + kColA + (uint32_t)s * 32u + part * 16u, a);
+          tmem_st_wait();
+        }
+        // the packed slot goes back to the producer only after the stores that consumed its words
+        if (j == kTaWChunk - 1 || kb + 1 == num_kb) {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_w_empty(ws));
+        }
+        tc_fence_before();
+        mbar_arrive(bar_full(s));   // every thread arrives itself (also on abort)
+      }
+      if (vec_sb) {
+        sv_cur = sv_nxt; bv_cur = bv_nxt;
+        load_sb8(sv_nxt, bv_nxt, kb0 + 2 * kUnroll);
+      }
+    }
+    // ---- epilogue: D[weight row][token] in TMEM -> y[token][weight row] ------------------------------------------
+    const bool acc_ok = ok && mbar_wait(bar_accum, 0u, p.status, 5u, abort_flag);
+    tc_fence_after();
+    if (acc_ok) {
+      const uint32_t n = n0 + r_tile;
+      const int half = (int)part;                        // the two warps of a quarter take alternate token blocks
+#pragma unroll 1
+      for (int cb = half; cb < NT / 32; cb += 2) {
+        uint32_t v[32];
+        tmem_ld32(tmem_base + lane_base + (uint32_t)(cb * 32), v);
+        tmem_ld_wait();
+        const uint32_t m_first = m0 + cb * 32;
+        if (n < p.N) {
+          if (p.out_f32) {
+            float* dst = reinterpret_cast<float*>(p.Y) + (size_t)m_first * p.N + n;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (m_first + i < p.M) dst[(size_t)i * p.N] = __uint_as_float(v[i]);
+          } else {
+            __half* dst = reinterpret_cast<__half*>(p.Y) + (size_t)m_first * p.N + n;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (m_first + i < p.M) dst[(size_t)i * p.N] = __float2half_rn(__uint_as_float(v[i]));
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// ---- host side ---------------------------------------------------------------------------------------------
+typedef CUresult (*TaEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static TaEncodeFn ta_encode_fn() {
+  static TaEncodeFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<TaEncodeFn>(ptr);
+  }
+  return fn;
+}
+
+template <int NT, bool AFFINE>
+static cudaError_t launch_ta_one(const CUtensorMap& tx, const CUtensorMap& tw, const GemmTaParams& p, cudaStream_t st) {
+  auto kern = gemm_w4_ta_kernel<NT, AFFINE>;
+  constexpr int smem = GemmTaSmem<NT>::kTotal + 1024;
+  static bool attr_set[16] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 16 && !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    attr_set[dev] = true;
+  }
+  dim3 grid((p.N + kTaRows - 1) / kTaRows, (p.M + NT - 1) / NT);
+  kern<<<grid, kTaThreads, smem, st>>>(tx, tw, p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_gemm_w4_ta(const uint32_t* W, const __half* S, const __half* B, const __half* X, void* Y, uint32_t M,
+                              uint32_t N, uint32_t K, uint32_t group_shift, bool out_f32, uint32_t* status, cudaStream_t st) {
+  TaEncodeFn enc = ta_encode_fn();
+  if (!enc) return cudaErrorNotSupported;
+  const cuuint32_t estr[2] = {1, 1};
+  CUtensorMap tx, tw;
+  const cuuint64_t xdims[2] = {K, M};
+  const cuuint64_t xstrides[1] = {(cuuint64_t)K * 2};
+  const cuuint32_t xbox[2] = {(cuuint32_t)kGemmBK, 128};
+  CUresult r = enc(&tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(X), xdims, xstrides, xbox, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+  const cuuint64_t wdims[2] = {K / 8, N};
+  const cuuint64_t wstrides[1] = {(cuuint64_t)(K / 8) * 4};
+  const cuuint32_t wbox[2] = {32, (cuuint32_t)kTaRows};
+  r = enc(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint32_t*>(W), wdims, wstrides, wbox, estr,
+          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+  GemmTaParams p;
+  p.S = S; p.B = B; p.Y = Y;
+  p.M = M; p.N = N; p.K = K; p.SPR = K >> group_shift; p.group_shift = group_shift;
+  p.out_f32 = out_f32 ? 1u : 0u;
+  p.status = status;
+  const bool affine = B != nullptr;
+  if (M > 128) return affine ? launch_ta_one<256, true>(tx, tw, p, st) : launch_ta_one<256, false>(tx, tw, p, st);
+  return affine ? launch_ta_one<128, true>(tx, tw, p, st) : launch_ta_one<128, false>(tx, tw, p, st);
+}
+
+}  // namespace ztvm

@@ -64,6 +64,11 @@ cudaError_t launch_moe_grouped_static(const GemvParams& g, uint32_t tokens, uint
                                       cudaStream_t st);
 cudaError_t launch_moe_tc_static(const GemvParams& g, uint32_t tokens, uint32_t slots, int sm_count, cudaStream_t st);
 
+// The same GEMM with the dequantised weights as the A operand in tensor memory and the activations as the only
+// shared-memory operand (ztvm_gemm_ta.cu): the default for M > 8; launch_gemm_w4 stays selectable for comparison.
+cudaError_t launch_gemm_w4_ta(const uint32_t* W, const __half* S, const __half* B, const __half* X, void* Y, uint32_t M,
+                              uint32_t N, uint32_t K, uint32_t group_shift, bool out_f32, uint32_t* status, cudaStream_t st);
+
 cudaError_t launch_unpack_codes(const uint32_t* W, uint8_t* codes, uint32_t N, uint32_t K, int bits, cudaStream_t st);
 cudaError_t launch_dequant(const uint32_t* W, const __half* S, const __half* B, void* out, uint32_t N, uint32_t K,
                            int bits, uint32_t group_shift, bool affine, bool as_f16, cudaStream_t st);
