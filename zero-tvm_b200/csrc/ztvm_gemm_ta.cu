@@ -361,7 +361,10 @@ cudaError_t launch_gemm_w4_ta(const uint32_t* W, const __half* S, const __half* 
   p.out_f32 = out_f32 ? 1u : 0u;
   p.status = status;
   const bool affine = B != nullptr;
-  if (M > 128) return affine ? launch_ta_one<256, true>(tx, tw, p, st) : launch_ta_one<256, false>(tx, tw, p, st);
+  // 256 tokens per instruction unless that leaves most SMs without a tile (M = 256 on 8192 rows: 64 CTAs of 256 tokens
+  // or 128 CTAs of 128)
+  const uint64_t ctas256 = (uint64_t)((N + kTaRows - 1) / kTaRows) * ((M + 255) / 256);
+  if (M > 128 && (M > 256 || ctas256 >= 111)) return affine ? launch_ta_one<256, true>(tx, tw, p, st) : launch_ta_one<256, false>(tx, tw, p, st);
   return affine ? launch_ta_one<128, true>(tx, tw, p, st) : launch_ta_one<128, false>(tx, tw, p, st);
 }
 
