@@ -89,6 +89,9 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
     mbar_init(bar_accum, 1);
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    // Programmatic dependent launch: nothing before this point (nor the weight / scale loads of the other warps)
+    // touches what the previous kernel in the stream may write; the activations may be its output.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     for (uint32_t kb = 0; kb < (uint32_t)kGemmStages && kb < num_kb; ++kb) {
       mbar_arrive_expect_tx(bar_full((int)kb), (uint32_t)L::kABytes);
 #pragma unroll
@@ -117,6 +120,7 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (warp == 0) {
     // ================= TMA producer =================
@@ -311,6 +315,7 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
     // ---- epilogue: TMEM -> registers -> y ---------------------------------------------------------
     const bool acc_ok = ok && mbar_wait(bar_accum, 0u, p.status, 5u, abort_flag);
     tc_fence_after();
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // y may still be read by the previous kernel in the stream
     if (acc_ok && p.tma_store) {
       // f16 output: registers -> shared memory in the 128-byte swizzle (two 64-column halves per 128-token block,
       // in the activation ring, which is idle once the accumulators are final) -> one TMA store per half.
@@ -428,9 +433,17 @@ static cudaError_t launch_gemm_one(const CUtensorMap& tmap, const CUtensorMap& t
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
   }
-  dim3 grid((p.N + BN - 1) / BN, (p.M + MB * 128 - 1) / (MB * 128));
-  kern<<<grid, kGemmThreads, smem, st>>>(tmap, tmap_w, tmap_y, p);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((p.N + BN - 1) / BN, (p.M + MB * 128 - 1) / (MB * 128));
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, tmap, tmap_w, tmap_y, p);
 }
 
 bool gemm_w4_supported(int bits, uint32_t group, uint32_t K) {

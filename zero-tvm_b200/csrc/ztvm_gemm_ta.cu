@@ -95,6 +95,9 @@ gemm_w4_ta_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
     mbar_init(bar_accum, 1);
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    // Programmatic dependent launch: everything before this point (and the weight / scale loads of the other warps)
+    // touches nothing the previous kernel in the stream may write; the activations may be its output.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     for (uint32_t kb = 0; kb < (uint32_t)kTaStages && kb < num_kb; ++kb) {
       mbar_arrive_expect_tx(bar_full((int)kb), (uint32_t)L::kXBytes);
 #pragma unroll
@@ -122,6 +125,7 @@ gemm_w4_ta_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (warp == 0) {
     // ================= TMA producer: activations =================
@@ -272,6 +276,7 @@ gemm_w4_ta_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
     // ---- epilogue: D[weight row][token] in TMEM -> y[token][weight row] ------------------------------------------
     const bool acc_ok = ok && mbar_wait(bar_accum, 0u, p.status, 5u, abort_flag);
     tc_fence_after();
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // y may still be read by the previous kernel in the stream
     if (acc_ok) {
       const uint32_t n = n0 + r_tile;
       const int half = (int)part;                        // the two warps of a quarter take alternate token blocks
@@ -330,9 +335,17 @@ static cudaError_t launch_ta_one(const CUtensorMap& tx, const CUtensorMap& tw, c
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
   }
-  dim3 grid((p.N + kTaRows - 1) / kTaRows, (p.M + NT - 1) / NT);
-  kern<<<grid, kTaThreads, smem, st>>>(tx, tw, p);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((p.N + kTaRows - 1) / kTaRows, (p.M + NT - 1) / NT);
+  cfg.blockDim = dim3(kTaThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, tx, tw, p);
 }
 
 cudaError_t launch_gemm_w4_ta(const uint32_t* W, const __half* S, const __half* B, const __half* X, void* Y, uint32_t M,
