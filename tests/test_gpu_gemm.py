@@ -99,3 +99,19 @@ def test_exact_properties(backend, dev):
     perm = np.random.default_rng(0).permutation(256)
     yp = run_gemm(backend, dev, dict(p, x=p["x"][perm]))
     assert np.array_equal(yp.view(np.uint16), y1[perm].view(np.uint16))
+
+
+@pytest.mark.parametrize("M", [100, 130, 300])
+def test_f32_output_through_the_c_abi(M, backend, dev, oracle_c):
+    """out_f32 with M > 8 (no reference GEMM entry writes f32, the C ABI allows it): the shared-memory-operand kernel
+    (M <= 128) and both tile widths of the weights-in-TMEM kernel, ragged N."""
+    N, K = 200, 512
+    p = z.synth.projection(N, K, M=M, seed=40 + M)
+    y = dev.empty((M + 1, N), np.float32, fill=-77.0)
+    backend.ctx.int4_matmul(z.MmDesc(K, N, M, 64, 4, 1, 1), y, dev.put(p["x"]), dev.put(p["scales"]), dev.put(p["W"]),
+                            dev.put(p["biases"]))
+    backend.ctx.sync()
+    out = dev.get(y)
+    assert backend.ctx.device_errors() == 0
+    assert (out[M:] == -77.0).all()
+    check(out[:M], p, oracle_c)
