@@ -1,4 +1,6 @@
-// Prefill GEMM (M > 8) for 4-bit group-quantised weights on the 5th-generation tensor cores.
+// Prefill GEMM for 4-bit group-quantised weights on the 5th-generation tensor cores, both operands in shared memory.
+// Serves 8 < M <= 128 (64-row weight tiles give twice as many CTAs as ztvm_gemm_ta.cu's 128-row tiles) and, with
+// ZTVM_GEMM=sm, every M for comparison.
 //
 //   y[m, n] = sum_k x[m, k] * W16[n, k],   W16 = f16_rne(fl32(s * q + b))   (or s * (q - 7))
 //
@@ -12,9 +14,9 @@
 //               per 128-token block, accumulators live in TMEM; tcgen05.commit releases the ring slot
 //   warp 2      TMA producer for packed weights: tiles W[BN rows x 32 words] (= 256 codes, four k blocks, whole
 //               128-byte lines per row) into a ring of its own, so the code stream runs far ahead of its use
-//   warps 3..10 dequantisers: two threads per weight row of the tile; per 64-wide k block a thread reads 16 bytes
-//               of codes from shared memory and the group's scale/bias, builds 32 f16 weights with the SAME device
-//               function the parity hook uses, and writes them in the tensor core's K-major 128B-swizzled layout.
+//   warps 3..10 dequantisers, as two groups of four warps on alternate k blocks: per 64-wide k block a thread reads
+//               its row's codes from shared memory and the group's scale/bias, builds the f16 weights with the SAME
+//               device function the parity hook uses, and writes them in the tensor core's K-major 128B-swizzled layout.
 //               After the main loop the same eight warps drain TMEM (tcgen05.ld) and store y.
 // Every mbarrier wait is bounded (about a second); a wait that runs out raises a status word, the roles
 // stop, in-flight copies are waited for (bounded), TMEM is freed and the kernel returns.
