@@ -168,3 +168,20 @@ def test_backend_dispatch_argument_errors_need_no_gpu():
         be.dispatch("int4_matmul_tiled_affine_moe", [1, 2, 3, 4, [256, 32, 8], 5])  # no ids / short PODArgs
     with pytest.raises(ValueError):
         be.dispatch("int4_matmul_batched_dyn_affine", [1, 2, 3, 4, [256, 32, 8], 5])  # no M_ROWS
+
+
+def test_bench_workload_parsing_and_algorithmic_bytes():
+    """bench.py's shape: syntax and its algorithmic-byte count (weights + scales + biases + activations + outputs)."""
+    import importlib.util
+    import os
+    spec = importlib.util.spec_from_file_location("ztvm_bench", os.path.join(os.path.dirname(os.path.dirname(__file__)), "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    assert bench.workload_shapes("shape:12288x4096x4") == [("W[12288,4096] M=4", 12288, 4096, 4, False)]
+    assert bench.workload_shapes("shape:151936x4096x1xf32")[0][-1] is True
+    assert bench.workload_shapes("prefill_gemm_m512")[0][1:4] == (8192, 2048, 512)
+    assert len(bench.workload_shapes("decode_layer_set")) == 8
+    # config 0: 8192 x 2048 int4 g64 affine, M = 1, f16 out
+    assert bench.algorithmic_bytes(8192, 2048, 1) == 8192 * 1024 + 2 * 8192 * 32 * 2 + 2048 * 2 + 8192 * 2
+    with pytest.raises(SystemExit):
+        bench.workload_shapes("no_such_workload")
