@@ -255,6 +255,7 @@ ztvm_status ztvm_int4_matmul(ztvm_ctx* ctx, const ztvm_mm_desc* d, void* y, cons
                      : static_cast<void*>(static_cast<__half*>(y) + (size_t)m0 * d->N);
     const bool want_tc = ctx->gemv_path == 0 || (ctx->gemv_path == 3 && dd.M > 1);
     if (want_tc && ztvm::gemv_tc_supported(p, (int)d->bits, ctx->sm_count)) ZTVM_CUDA(ztvm::launch_gemv_tc(p, ctx->sm_count, st));
+    else if (want_tc && ztvm::gemv_tc3_supported(p, (int)d->bits, ctx->sm_count)) ZTVM_CUDA(ztvm::launch_gemv_tc3(p, ctx->sm_count, st));
     else if (use_mma(ctx, d, dd.M)) ZTVM_CUDA(ztvm::launch_gemv_mma(p, false, 1, 1, st));
     else ZTVM_CUDA(ztvm::launch_gemv(p, (int)d->bits, false, 1, 1, ctx->sm_count, st));
   }

@@ -40,6 +40,10 @@ cudaError_t launch_gemv_mma(GemvParams p, bool moe, uint32_t tokens, uint32_t sl
 bool gemv_tc_supported(const GemvParams& p, int bits, int sm_count);
 cudaError_t launch_gemv_tc(const GemvParams& p, int sm_count, cudaStream_t st);
 
+// 3-bit / group-64 weights, M = 1, persistent matrix-unit GEMV (ztvm_gemv_tc3.cu).
+bool gemv_tc3_supported(const GemvParams& p, int bits, int sm_count);
+cudaError_t launch_gemv_tc3(const GemvParams& p, int sm_count, cudaStream_t st);
+
 // 4-bit weights, M > 8: tcgen05 GEMM with TMEM accumulators (ztvm_gemm.cu). status[0] receives a non-zero code
 // if a pipeline wait inside the kernel ran out.
 bool gemm_w4_supported(int bits, uint32_t group, uint32_t K);
