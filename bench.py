@@ -11,7 +11,7 @@ Workloads
   prefill_gemm_m512  X[512,2048] f16 times int4 W[8192,2048] (group 64, affine), f16 out. TFLOP/s. (default)
   decode_gemv        x[1,2048] times the same weight format, GB/s of algorithmic bytes.
   decode_layer_set   the 8B-class projections at M=1 (q,k,v,o,gate,up,down,lm_head), GB/s.
-  shape:NxKxM[xf32]  one projection of any size (GB/s for M <= 8, TFLOP/s above); used for profiles and sweeps.
+  shape:NxKxM[xf32][xq3]  one projection of any size (GB/s for M <= 8, TFLOP/s above; q3 = 3-bit codes): profiles, sweeps.
 
   layer_set_nshard   the same eight projections with their output rows sharded over the ranks and one all-gather
                      per projection (strong scaling, GB/s of the whole layer set); --m-rows 1|4
@@ -41,7 +41,11 @@ METRIC = "int4 matmul HBM GB/s (decode M=1) and TFLOP/s (prefill M=512) vs roofl
 L2_BYTES = 126 * 1024 * 1024
 
 
-def algorithmic_bytes(N, K, M, bits=4, group=64, affine=True, out_bytes=2):
+BITS = 4   # code width of the timed workload: 3 for shape:...xq3, else 4
+
+
+def algorithmic_bytes(N, K, M, bits=None, group=64, affine=True, out_bytes=2):
+    bits = BITS if bits is None else bits
     """weights + scales (+ biases) + activations + outputs, each touched once."""
     return N * K * bits // 8 + (2 if affine else 1) * (N * K // group) * 2 + M * K * 2 + M * N * out_bytes
 
@@ -114,8 +118,10 @@ def workload_shapes(name):
     if name.startswith("shape:"):      # shape:NxKxM (f16 out) or shape:NxKxMxf32 — any one projection, e.g. for profiling
         parts = name[6:].split("x")
         N, K, M = (int(v) for v in parts[:3])
-        f32 = len(parts) > 3 and parts[3] == "f32"
-        return [(f"W[{N},{K}] M={M}", N, K, M, f32)]
+        f32 = "f32" in parts[3:]
+        global BITS
+        BITS = 3 if "q3" in parts[3:] else 4
+        return [(f"W{'3' if BITS == 3 else ''}[{N},{K}] M={M}", N, K, M, f32)]
     raise SystemExit(f"unknown workload {name}")
 
 
@@ -129,7 +135,7 @@ def make_sets(shapes, seed, torch, device):
     for _ in range(R):
         one = []
         for _, N, K, M, f32 in shapes:
-            W = torch.randint(-2**31, 2**31 - 1, (N, K // 8), dtype=torch.int32, device=device, generator=g)
+            W = torch.randint(-2**31, 2**31 - 1, (N, K * BITS // 32), dtype=torch.int32, device=device, generator=g)
             s = (torch.randn((N, K // 64), device=device, generator=g) * 0.01).abs().to(torch.float16)
             b = (torch.randn((N, K // 64), device=device, generator=g) * 0.05).to(torch.float16)
             y = torch.empty((M, N), dtype=torch.float32 if f32 else torch.float16, device=device)
@@ -320,7 +326,7 @@ def quick_device_rate(ctx, torch, device, z, workload, steps, warmup, seed=4321)
     shapes = workload_shapes(workload)
     sets, R = make_sets(shapes, seed, torch, device)
     xs = [torch.randn((M, K), device=device).to(torch.float16) for _, N, K, M, _ in shapes]
-    descs = [z.MmDesc(K, N, M, 64, 4, 1, int(f32)) for _, N, K, M, f32 in shapes]
+    descs = [z.MmDesc(K, N, M, 64, BITS, 1, int(f32)) for _, N, K, M, f32 in shapes]
     stream = torch.cuda.Stream(device)
 
     def one_pass():
@@ -393,10 +399,12 @@ def main():
     ctx = z.Context(local)
 
     shapes = workload_shapes(args.workload)
+    if BITS != 4:
+        args.no_cpu_baseline = True     # the CPU sample is the 4-bit reference-order matmul
     is_gemm = shapes[0][3] > 8
     sets, R = make_sets(shapes, 1234 + rank, torch, device)
     xs = [torch.randn((M, K), device=device).to(torch.float16) for _, N, K, M, _ in shapes]
-    descs = [z.MmDesc(K, N, M, 64, 4, 1, int(f32)) for _, N, K, M, f32 in shapes]
+    descs = [z.MmDesc(K, N, M, 64, BITS, 1, int(f32)) for _, N, K, M, f32 in shapes]
     stream = torch.cuda.Stream(device)
 
     def one_pass():
@@ -476,7 +484,7 @@ def main():
         zc.build()
         rows = min(M, 4)
         y64 = zc.matmul_f64(xs[0][:rows].cpu().numpy(), W.cpu().numpy().view(np.uint32), s.cpu().numpy(),
-                            b.cpu().numpy(), 64, w16=is_gemm)
+                            b.cpu().numpy(), 64, BITS, w16=is_gemm)
         floor = (1e-2 if is_gemm else 1e-3) * float(np.sqrt(np.mean(y64 * y64)))
         err = float(np.max(np.abs(yh[:rows] - y64) / np.maximum(np.abs(y64), floor)))
         verified = {"rows": rows, "max_rel_err": err, "ok": bool(err <= 2e-3 and np.abs(yh).max() > 0)}
@@ -522,7 +530,7 @@ def main():
         "metric": METRIC, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f16 x int4 -> f32 accumulate", "data": "synthetic",
-        "config": {"workload": args.workload, "shapes": [s_[0] for s_ in shapes], "group": 64, "bits": 4,
+        "config": {"workload": args.workload, "shapes": [s_[0] for s_ in shapes], "group": 64, "bits": BITS,
                    "rotation_sets": R_rot, "passes_per_step": passes, "rotation_bytes": int(bytes_step // passes),
                    "l2": "inputs larger than L2: weight sets rotate, 4x L2 per step",
                    "parallelism": "replicas" if world > 1 else "single"},
