@@ -134,6 +134,15 @@ def test_int3_gemv_config(backend, dev, oracle_c):
     check_y(y, p, oracle_c)
 
 
+@pytest.mark.parametrize("N,K", [(13, 256), (100, 768), (301, 8192), (2000, 12288)])
+def test_int3_streaming_kernel_shapes(N, K, backend, dev, oracle_c):
+    """The 3-bit streaming GEMV over one, three and more than sixteen K slices (the last two run several K tiles
+    with their running sums in shared memory), rows that do not fill the 16-row tiles."""
+    p = z.synth.projection(N, K, bits=3, seed=N)
+    check_y(run_matmul(backend, dev, p), p, oracle_c)
+    check_y(run_matmul(backend, dev, p, out_f32=True), p, oracle_c)
+
+
 @pytest.mark.parametrize("name,N,K,f32", z.synth.DENSE_LAYER_SET)
 @pytest.mark.parametrize("M", [1, 4])
 def test_dense_layer_set(name, N, K, f32, M, backend, dev, oracle_c):
