@@ -10,7 +10,7 @@ graph so host launch cost does not enter the device-timed number. Rank 0 prints 
 Workloads
   prefill_gemm_m512  X[512,2048] f16 times int4 W[8192,2048] (group 64, affine), f16 out. TFLOP/s. (default)
   decode_gemv        x[1,2048] times the same weight format, GB/s of algorithmic bytes.
-  decode_layer_set   the 8B-class projections at M=1 (q,k,v,o,gate,up,down,lm_head), GB/s.
+  decode_layer_set   the 8B-class projections at M=1 (q,k,v,o,gate,up,down,lm_head), GB/s; decode_layer_set_m4: at M=4.
   shape:NxKxM[xf32][xq3]  one projection of any size (GB/s for M <= 8, TFLOP/s above; q3 = 3-bit codes): profiles, sweeps.
 
   layer_set_nshard   the same eight projections with their output rows sharded over the ranks and one all-gather
@@ -113,8 +113,9 @@ def workload_shapes(name):
         return [("W[8192,2048] M=512", 8192, 2048, 512, False)]
     if name == "decode_gemv":
         return [("W[8192,2048] M=1", 8192, 2048, 1, False)]
-    if name == "decode_layer_set":
-        return [(n, N, K, 1, f32) for n, N, K, f32 in z.synth.DENSE_LAYER_SET]
+    if name in ("decode_layer_set", "decode_layer_set_m4"):
+        M = 4 if name.endswith("_m4") else 1
+        return [(n, N, K, M, f32) for n, N, K, f32 in z.synth.DENSE_LAYER_SET]
     if name.startswith("shape:"):      # shape:NxKxM (f16 out) or shape:NxKxMxf32 — any one projection, e.g. for profiling
         parts = name[6:].split("x")
         N, K, M = (int(v) for v in parts[:3])
