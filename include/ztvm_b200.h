@@ -163,6 +163,17 @@ ZTVM_API ztvm_status ztvm_moe_route_topk(ztvm_ctx* ctx, uint32_t E, uint32_t K, 
                                 uint32_t tokens, uint32_t* ids, float* scores, const float* logits,
                                 void* stream);
 
+/* Dispatch plan of the expert-parallel form (experts dealt to ranks in contiguous runs of experts_per_rank): sorts
+ * the (token, slot) pairs of ids u32[tokens][ids_stride] (first `slots` entries of each row) by the rank that owns
+ * their expert. order i64[tokens*slots] = pair indices (token*slots + slot) in destination order, local_expert
+ * i32[...] = the pair's expert index inside its owner's stack, send_counts i64[world] = pairs per destination. Ids
+ * outside [0, experts) are counted (ztvm_device_errors) and left out: the filled prefix of order / local_expert has
+ * sum(send_counts) entries. The order inside one expert is not deterministic. No counterpart in the reference (it
+ * runs on one device); uses the context's plan buffer like ztvm_int4_matmul_moe. */
+ZTVM_API ztvm_status ztvm_moe_dispatch_plan(ztvm_ctx* ctx, const uint32_t* ids, uint32_t tokens, uint32_t slots,
+                                   uint32_t ids_stride, uint32_t experts, uint32_t experts_per_rank, uint32_t world,
+                                   int64_t* order, int32_t* local_expert, int64_t* send_counts, void* stream);
+
 /* h[r][i] = f16(up * gate * 1/(1+exp(-gate))) over rows of [gate(ffn) | up(ffn)] f16.
  * Replaces silu_mul (src/compiler/shaders/silu_mul.wgsl:26-44). */
 ZTVM_API ztvm_status ztvm_silu_mul(ztvm_ctx* ctx, uint32_t rows, uint32_t ffn, void* h, const void* gate_up, void* stream);

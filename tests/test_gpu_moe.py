@@ -247,3 +247,27 @@ def test_expert_parallel_form_on_one_rank_matches_the_seven_dispatches(T, backen
     torch.cuda.synchronize()
     got = y.cpu().numpy().astype(np.float64)
     assert np.abs(got - ref).max() <= 5e-3 * np.abs(ref).max()
+
+
+def test_dispatch_plan_on_the_device_matches_the_tensor_op_plan(backend, dev):
+    """ztvm_moe_dispatch_plan against the plan recomputed on the host: same pairs per destination, a
+    permutation of all pairs in destination order, the right local expert for every pair."""
+    import torch
+    from zero_tvm_b200 import sharded
+    T, K, E, world = 300, 8, 64, 4
+    epr = E // world
+    rng = np.random.default_rng(17)
+    ids_full = np.stack([rng.permutation(E)[:K + 1] for _ in range(T)]).astype(np.uint32)   # K routed + one more column
+    ids_full[:, K] = E
+    t = dev.put(ids_full)
+    k = sharded.CudaKernels(backend)
+    order, local, send = k.dispatch_plan(t[:, :K], epr, world)
+    torch.cuda.synchronize()
+    assert backend.ctx.device_errors() == 0
+    order, local, send = order.cpu().numpy(), local.cpu().numpy(), send.cpu().numpy()
+    flat = ids_full[:, :K].reshape(-1).astype(np.int64)
+    assert np.array_equal(send, np.bincount(flat // epr, minlength=world))
+    assert np.array_equal(np.sort(order), np.arange(T * K))
+    dest = flat[order] // epr
+    assert (np.diff(dest) >= 0).all()
+    assert np.array_equal(local, (flat[order] % epr).astype(np.int32))

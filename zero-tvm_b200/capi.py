@@ -15,7 +15,7 @@ LIB_PATH = os.path.join(_HERE, "lib", "libztvm_b200.so")
 SYMBOLS = [
     "ztvm_version", "ztvm_status_string", "ztvm_init", "ztvm_destroy", "ztvm_last_error", "ztvm_sync",
     "ztvm_int4_matmul", "ztvm_int4_matmul_multi", "ztvm_int4_matmul_host", "ztvm_int4_matmul_moe", "ztvm_int4_matmul_moe_noalloc",
-    "ztvm_moe_route_topk", "ztvm_silu_mul",
+    "ztvm_moe_route_topk", "ztvm_moe_dispatch_plan", "ztvm_silu_mul",
     "ztvm_moe_combine", "ztvm_unpack_codes", "ztvm_dequant", "ztvm_device_errors",
 ]
 
@@ -66,6 +66,7 @@ def load() -> C.CDLL:
         "ztvm_int4_matmul_moe": [vp, C.POINTER(MoeDesc), vp, vp, vp, vp, vp, vp, vp],
         "ztvm_int4_matmul_moe_noalloc": [vp, C.POINTER(MoeDesc), vp, vp, vp, vp, vp, vp, vp],
         "ztvm_moe_route_topk": [vp, u32, u32, u32, u32, u32, vp, vp, vp, vp],
+        "ztvm_moe_dispatch_plan": [vp, vp, u32, u32, u32, u32, u32, u32, vp, vp, vp, vp],
         "ztvm_silu_mul": [vp, u32, u32, vp, vp, vp],
         "ztvm_moe_combine": [vp, u32, u32, u32, vp, vp, vp, vp],
         "ztvm_unpack_codes": [vp, C.POINTER(MmDesc), vp, vp, vp],
@@ -158,6 +159,11 @@ class Context:
     def moe_route_topk(self, E, K, norm_topk, has_shared, tokens, ids, scores, logits, stream=None):
         check(self._lib.ztvm_moe_route_topk(self.handle, E, K, int(norm_topk), int(has_shared), tokens, ptr(ids),
                                             ptr(scores), ptr(logits), stream_ptr(stream)))
+
+    def moe_dispatch_plan(self, ids, tokens, slots, ids_stride, experts, experts_per_rank, world, order, local_expert,
+                          send_counts, stream=None):
+        check(self._lib.ztvm_moe_dispatch_plan(self.handle, ptr(ids), tokens, slots, ids_stride, experts, experts_per_rank,
+                                               world, ptr(order), ptr(local_expert), ptr(send_counts), stream_ptr(stream)))
 
     def silu_mul(self, rows, ffn, h, gate_up, stream=None):
         check(self._lib.ztvm_silu_mul(self.handle, rows, ffn, ptr(h), ptr(gate_up), stream_ptr(stream)))

@@ -451,6 +451,40 @@ ztvm_status ztvm_moe_route_topk(ztvm_ctx* ctx, uint32_t E, uint32_t K, uint32_t 
   return ZTVM_OK;
 }
 
+ztvm_status ztvm_moe_dispatch_plan(ztvm_ctx* ctx, const uint32_t* ids, uint32_t tokens, uint32_t slots, uint32_t ids_stride,
+                                   uint32_t experts, uint32_t experts_per_rank, uint32_t world, int64_t* order,
+                                   int32_t* local_expert, int64_t* send_counts, void* stream) {
+  ztvm_status s = check_ctx(ctx);
+  if (s) return s;
+  if (!ids || !order || !local_expert || !send_counts) return fail(ZTVM_ERR_NULL_POINTER, "ids/order/local_expert/send_counts must be non-NULL");
+  if (experts == 0 || experts > 1024) return fail(ZTVM_ERR_TOO_LARGE, "experts=%u: 1..1024 supported", experts);
+  if (experts_per_rank == 0 || world == 0 || (uint64_t)experts_per_rank * world < experts)
+    return fail(ZTVM_ERR_BAD_DIMS, "experts_per_rank=%u x world=%u does not cover experts=%u", experts_per_rank, world, experts);
+  if (slots == 0 || ids_stride < slots) return fail(ZTVM_ERR_BAD_DIMS, "need 1 <= slots <= ids_stride (slots=%u, ids_stride=%u)", slots, ids_stride);
+  const uint64_t pairs = (uint64_t)tokens * slots;
+  if (pairs >= (1ull << 31)) return fail(ZTVM_ERR_TOO_LARGE, "tokens*slots=%llu", (unsigned long long)pairs);
+  cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : ctx->stream;
+  if (tokens == 0) {
+    ZTVM_CUDA(cudaMemsetAsync(send_counts, 0, (size_t)world * 8, st));
+    return ZTVM_OK;
+  }
+  const size_t need = ztvm::moe_grouped_scratch_bytes(experts, (uint32_t)pairs);
+  if (ctx->d_ws_bytes < need) {
+    ZTVM_CUDA(cudaDeviceSynchronize());
+    if ((s = grow(&ctx->d_ws, &ctx->d_ws_bytes, need, false))) return s;
+  }
+  ztvm::GemvParams p;
+  memset(&p, 0, sizeof(p));
+  p.ids = ids;
+  p.experts = experts;
+  p.ids_stride = ids_stride;
+  p.err_counter = ctx->err_counter;
+  ZTVM_CUDA(ztvm::launch_moe_dispatch_plan(p, tokens, slots, experts_per_rank, world, static_cast<uint32_t*>(ctx->d_ws),
+                                           reinterpret_cast<long long*>(order), local_expert,
+                                           reinterpret_cast<long long*>(send_counts), st));
+  return ZTVM_OK;
+}
+
 ztvm_status ztvm_silu_mul(ztvm_ctx* ctx, uint32_t rows, uint32_t ffn, void* h, const void* gate_up, void* stream) {
   ztvm_status s = check_ctx(ctx);
   if (s) return s;

@@ -61,6 +61,10 @@ cudaError_t launch_moe_grouped(const GemvParams& g, uint32_t tokens, uint32_t sl
 bool moe_tc_supported(const GemvParams& g, int bits);
 cudaError_t launch_moe_tc(const GemvParams& g, uint32_t tokens, uint32_t slots, uint32_t* scratch, int sm_count,
                           cudaStream_t st);
+// Dispatch plan of the expert-parallel form: pairs in owner-rank order, their local expert index, pairs per rank.
+cudaError_t launch_moe_dispatch_plan(const GemvParams& g, uint32_t tokens, uint32_t slots, uint32_t epr, uint32_t world,
+                                     uint32_t* scratch, long long* order, int* local_expert, long long* send_counts,
+                                     cudaStream_t st);
 // The same launch with the planning scratch in a fixed array inside the module (no allocation anywhere on the path).
 // `moe_static_scratch_fits` says whether a problem fits that array; the launcher refuses one that does not.
 bool moe_static_scratch_fits(uint32_t experts, uint64_t pairs);

@@ -370,6 +370,41 @@ cudaError_t launch_moe_plan(const GemvParams& g, uint32_t tokens, uint32_t slots
   return cudaGetLastError();
 }
 
+// ---- dispatch plan of the expert-parallel form ---------------------------------------------------------------------
+// After the plan: pairs sorted by expert are also sorted by the rank that owns the expert (experts are dealt to ranks in
+// contiguous runs of `epr`). order[i] = pair index, local_expert[i] = its expert's index inside the owner's stack,
+// send_counts[r] = pairs that travel to rank r.
+__global__ void moe_dispatch_finish_kernel(uint32_t E, uint32_t epr, uint32_t world, MoeScratch sc, long long* order,
+                                           int* local_expert, long long* send_counts) {
+  const uint32_t P = sc.offsets[E];
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < P; i += gridDim.x * blockDim.x) {
+    uint32_t lo = 0, hi = E;                       // the expert e with offsets[e] <= i < offsets[e + 1]
+    while (hi - lo > 1) {
+      const uint32_t mid = (lo + hi) >> 1;
+      if (sc.offsets[mid] <= i) lo = mid; else hi = mid;
+    }
+    order[i] = (long long)sc.sorted[i];
+    local_expert[i] = (int)(lo % epr);
+  }
+  if (blockIdx.x == 0)
+    for (uint32_t r = threadIdx.x; r < world; r += blockDim.x) {
+      const uint32_t a = min(r * epr, E), b = min((r + 1) * epr, E);
+      send_counts[r] = (long long)(sc.offsets[b] - sc.offsets[a]);
+    }
+}
+
+cudaError_t launch_moe_dispatch_plan(const GemvParams& g, uint32_t tokens, uint32_t slots, uint32_t epr, uint32_t world,
+                                     uint32_t* scratch, long long* order, int* local_expert, long long* send_counts,
+                                     cudaStream_t st) {
+  const uint32_t P = tokens * slots;
+  MoeScratch sc = moe_scratch_carve(scratch, g.experts, P);
+  cudaError_t e = launch_moe_plan(g, tokens, slots, sc, (uint32_t)kMoeBM, st);
+  if (e != cudaSuccess) return e;
+  const unsigned blocks = (P + 255) / 256 > 592 ? 592 : (P + 255) / 256;
+  moe_dispatch_finish_kernel<<<blocks ? blocks : 1, 256, 0, st>>>(g.experts, epr, world, sc, order, local_expert, send_counts);
+  return cudaGetLastError();
+}
+
 // ---- host side -----------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,

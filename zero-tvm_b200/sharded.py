@@ -58,6 +58,19 @@ class CudaKernels:
         self.be.ctx.int4_matmul_multi(MmDesc(K, N, M, 64, 4, 1, int(out_f32)), y_dsts, y_row_stride, x, s, W, b,
                                       stream=self._stream())
 
+    def dispatch_plan(self, ids_routed, experts_per_rank, world):
+        """ids_routed: an int32 [T, K] view (row stride allowed) of routed expert ids -> (order i64, local expert i32,
+        pairs per destination rank i64), all on the device."""
+        T, K = ids_routed.shape
+        assert ids_routed.stride(1) == 1
+        dev = ids_routed.device
+        order = torch.empty((T * K,), dtype=torch.int64, device=dev)
+        local_expert = torch.empty((T * K,), dtype=torch.int32, device=dev)
+        send = torch.empty((world,), dtype=torch.int64, device=dev)
+        self.be.ctx.moe_dispatch_plan(ids_routed, T, K, ids_routed.stride(0), experts_per_rank * world, experts_per_rank,
+                                      world, order, local_expert, send, stream=self._stream())
+        return order, local_expert, send
+
     def route_topk(self, ids, scores, logits, E, K, tokens):
         self.be.moe_router_topk(ids, scores, logits, E, K, True, True, tokens, stream=self._stream())
 
@@ -175,18 +188,27 @@ class DispatchPlan:
     local_expert: torch.Tensor  # [P] expert index inside the destination's stack, in send order
 
 
-def plan_dispatch(ids_routed: torch.Tensor, experts_per_rank: int, world: int, group=None) -> DispatchPlan:
-    """Buckets the routed (token, slot) pairs by the rank that owns their expert."""
-    flat = ids_routed.reshape(-1).to(torch.int64)
-    dest = torch.div(flat, experts_per_rank, rounding_mode="floor")
-    order = torch.argsort(dest, stable=True)
-    send = torch.bincount(dest, minlength=world)[:world]
+def plan_dispatch(ids_routed: torch.Tensor, experts_per_rank: int, world: int, group=None, kernels=None) -> DispatchPlan:
+    """Buckets the routed (token, slot) pairs by the rank that owns their expert.
+
+    `kernels.dispatch_plan`, when the kernels object has one, does the sort on the device in one call
+    (ztvm_moe_dispatch_plan); otherwise the same plan is built from tensor ops (any device: the CPU ranks of the tests).
+    Either way the split sizes have to reach the host: one device-to-host copy per step.
+    """
+    if kernels is not None and hasattr(kernels, "dispatch_plan"):
+        order, local_expert, send = kernels.dispatch_plan(ids_routed, experts_per_rank, world)
+    else:
+        flat = ids_routed.reshape(-1).to(torch.int64)
+        dest = torch.div(flat, experts_per_rank, rounding_mode="floor")
+        order = torch.argsort(dest, stable=True)
+        send = torch.bincount(dest, minlength=world)[:world]
+        local_expert = (flat[order] % experts_per_rank).to(torch.int32)
     if world > 1:
         recv = torch.empty_like(send)
         dist.all_to_all_single(recv, send, group=group)
     else:
         recv = send.clone()
-    return DispatchPlan(order, send.tolist(), recv.tolist(), (flat[order] % experts_per_rank).to(torch.int32))
+    return DispatchPlan(order, send.tolist(), recv.tolist(), local_expert)
 
 
 class ExpertParallelMoE:
@@ -217,7 +239,7 @@ class ExpertParallelMoE:
         ids = torch.empty((T, K + 1), dtype=torch.int32, device=dev)
         scores = torch.empty((T, K + 1), dtype=torch.float32, device=dev)
         self.k.route_topk(ids, scores, logits, self.E, K, T)
-        plan = plan_dispatch(ids[:, :K], self.epr, self.world, self.group)
+        plan = plan_dispatch(ids[:, :K], self.epr, self.world, self.group, kernels=self.k)
         # dispatch: activation rows and their local expert index, in destination order
         tok_of_pair = torch.div(plan.order, K, rounding_mode="floor")
         x_send = x.index_select(0, tok_of_pair)
