@@ -185,3 +185,30 @@ def test_bench_workload_parsing_and_algorithmic_bytes():
     assert bench.algorithmic_bytes(8192, 2048, 1) == 8192 * 1024 + 2 * 8192 * 32 * 2 + 2048 * 2 + 8192 * 2
     with pytest.raises(SystemExit):
         bench.workload_shapes("no_such_workload")
+
+
+def test_plan_dispatch_uses_a_kernels_hook_when_there_is_one():
+    """sharded.plan_dispatch: the tensor-op plan and a kernels object's dispatch_plan give interchangeable plans."""
+    import numpy as np
+    import torch
+    from zero_tvm_b200 import sharded
+    rng = np.random.default_rng(5)
+    ids = torch.from_numpy(rng.integers(0, 32, size=(20, 4)).astype(np.int32))
+    ref = sharded.plan_dispatch(ids, 8, 1)
+    assert ref.send_counts == [80] and ref.recv_counts == [80]
+    assert sorted(ref.order.tolist()) == list(range(80))
+    assert torch.equal(ref.local_expert, (ids.reshape(-1).to(torch.int64)[ref.order] % 8).to(torch.int32))
+
+    class Hook:
+        calls = 0
+
+        def dispatch_plan(self, ids_routed, epr, world):
+            Hook.calls += 1
+            flat = ids_routed.reshape(-1).to(torch.int64)
+            order = torch.argsort(flat, stable=True)            # by expert: also by owner rank
+            return order, (flat[order] % epr).to(torch.int32), torch.bincount(flat // epr, minlength=world)[:world]
+
+    got = sharded.plan_dispatch(ids, 8, 1, kernels=Hook())
+    assert Hook.calls == 1 and got.send_counts == ref.send_counts
+    assert sorted(got.order.tolist()) == list(range(80))
+    assert torch.equal(got.local_expert, (ids.reshape(-1).to(torch.int64)[got.order] % 8).to(torch.int32))
