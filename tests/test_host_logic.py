@@ -194,10 +194,10 @@ def test_plan_dispatch_uses_a_kernels_hook_when_there_is_one():
     from zero_tvm_b200 import sharded
     rng = np.random.default_rng(5)
     ids = torch.from_numpy(rng.integers(0, 32, size=(20, 4)).astype(np.int32))
-    ref = sharded.plan_dispatch(ids, 8, 1)
+    ref = sharded.plan_dispatch(ids, 32, 1)
     assert ref.send_counts == [80] and ref.recv_counts == [80]
     assert sorted(ref.order.tolist()) == list(range(80))
-    assert torch.equal(ref.local_expert, (ids.reshape(-1).to(torch.int64)[ref.order] % 8).to(torch.int32))
+    assert torch.equal(ref.local_expert, (ids.reshape(-1).to(torch.int64)[ref.order] % 32).to(torch.int32))
 
     class Hook:
         calls = 0
@@ -208,7 +208,7 @@ def test_plan_dispatch_uses_a_kernels_hook_when_there_is_one():
             order = torch.argsort(flat, stable=True)            # by expert: also by owner rank
             return order, (flat[order] % epr).to(torch.int32), torch.bincount(flat // epr, minlength=world)[:world]
 
-    got = sharded.plan_dispatch(ids, 8, 1, kernels=Hook())
+    got = sharded.plan_dispatch(ids, 32, 1, kernels=Hook())
     assert Hook.calls == 1 and got.send_counts == ref.send_counts
     assert sorted(got.order.tolist()) == list(range(80))
-    assert torch.equal(got.local_expert, (ids.reshape(-1).to(torch.int64)[got.order] % 8).to(torch.int32))
+    assert torch.equal(got.local_expert, (ids.reshape(-1).to(torch.int64)[got.order] % 32).to(torch.int32))
