@@ -142,9 +142,10 @@ ZTVM_API ztvm_status ztvm_int4_matmul_moe(ztvm_ctx* ctx, const ztvm_moe_desc* de
  *    ZTVM_ERR_TOO_LARGE. Only the two grouped kernels run here (there is no fall-back to the per-pair kernel):
  *    bits 4, group 64, and either K % 256 == 0, K <= 4096, N % 16 == 0 (streaming kernel) or K % 64 == 0,
  *    N % 128 == 0, output strides multiples of 8 elements, y 16-byte aligned (tensor-core tiles); input strides
- *    multiples of 8 elements. Anything else is ZTVM_ERR_UNSUPPORTED / ZTVM_ERR_ALIGNMENT. The kernel is chosen
- *    exactly as ztvm_int4_matmul_moe chooses it, so the results are those of that call on the same inputs, bit
- *    for bit.
+ *    multiples of 8 elements. Anything else is ZTVM_ERR_UNSUPPORTED / ZTVM_ERR_ALIGNMENT. From 128 pairs on
+ *    (and with the ZTVM_MOE_GROUPED knob unset) the kernel is chosen exactly as ztvm_int4_matmul_moe chooses it, so
+ *    the results are those of that call on the same inputs, bit for bit; below 128 pairs that call runs the per-pair
+ *    GEMV instead, and the two agree within the path's tolerance only.
  *  - The first call on a device looks up the array's device address and loads the kernels: make one call
  *    per device at start-up, before any stream capture.
  *  - There is ONE array per device, shared by every context and stream: two calls that overlap in time on
@@ -183,12 +184,25 @@ ZTVM_API ztvm_status ztvm_silu_mul(ztvm_ctx* ctx, uint32_t rows, uint32_t ffn, v
 ZTVM_API ztvm_status ztvm_moe_combine(ztvm_ctx* ctx, uint32_t tokens, uint32_t slots, uint32_t d, void* out,
                              const void* y_slots, const float* scores, void* stream);
 
-/* Parity hooks: materialise what the fused kernels never store, through the same device functions
- * the kernels inline. codes u8[N][K]; w_out f32[N][K] (as_f16 = 0: fl32(s*q+b), the GEMV / f32-staged
- * definition, int4_matmul.gen.ts:1001) or f16[N][K] (as_f16 = 1: f16_rne of that value, what the
- * tensor-core GEMM feeds the MMA; equals scripts/make-dsv2-layer-ref.py:108-116). desc->M is ignored. */
+/* Parity hooks: materialise what the fused kernels never store, each through the device function the corresponding
+ * production kernel inlines (so "codes and dequantised weights bit-exact" is a statement about the kernels that run).
+ *  - ztvm_unpack_codes: codes u8[N][K] through the arithmetic unpack (exact f16 integers for 4-bit, the 24-bit
+ *    window walk of int4_matmul.gen.ts:409-448 for 3-bit) that the CUDA-core GEMV, the tensor-core GEMMs and the
+ *    dequant hook use.
+ *  - ztvm_unpack_codes_streamed: the same codes as the streaming matrix-unit kernels consume them (persistent GEMV,
+ *    tiled GEMVs, streaming grouped MoE kernel, 3-bit GEMV): nibbles / 3-bit fields masked IN PLACE, which are f16
+ *    subnormals q * 2^-24 .. q * 2^-19, produced by the kernels' own mask functions and scaled back to integers.
+ *    Those kernels never form a dequantised weight: they multiply the in-place codes with the activations exactly and
+ *    fold scale and bias per group in f32 (y = sum_g s_g * dot_g + b_g * xsum_g, int4_matmul.gen.ts:388-408).
+ *    bits = 3 needs K % 64 == 0 (always true: K % group == 0).
+ *  - ztvm_dequant: w_out f32[N][K] (as_f16 = 0: fl32(s*q+b), the f32-staged definition of int4_matmul.gen.ts:1001, what
+ *    the CUDA-core GEMV multiplies) or f16[N][K] (as_f16 = 1: f16_rne of that value; equals
+ *    scripts/make-dsv2-layer-ref.py:108-116). For 4-bit weights the f16 form is produced by the word dequantiser the
+ *    tensor-core GEMMs (dense and grouped) inline. desc->M is ignored. */
 ZTVM_API ztvm_status ztvm_unpack_codes(ztvm_ctx* ctx, const ztvm_mm_desc* desc, uint8_t* codes, const void* packed_w,
                               void* stream);
+ZTVM_API ztvm_status ztvm_unpack_codes_streamed(ztvm_ctx* ctx, const ztvm_mm_desc* desc, uint8_t* codes,
+                                       const void* packed_w, void* stream);
 ZTVM_API ztvm_status ztvm_dequant(ztvm_ctx* ctx, const ztvm_mm_desc* desc, void* w_out, int32_t as_f16, const void* scales,
                          const void* packed_w, const void* biases, void* stream);
 

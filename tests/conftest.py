@@ -13,6 +13,44 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (B200); run with -m gpu")
 
 
+# ---- parity errors, both ways ------------------------------------------------------------------------------------
+# Every output comparison records the error graded with the reference's floor (the asserted one) and the pure
+# relative error max|y - ref| / |ref| beside it; the table is printed at the end of the run.
+_PARITY = {}
+_CURRENT = [None]
+
+
+def record_parity(floored: float, pure: float, label: str | None = None):
+    key = label or _CURRENT[0] or "?"
+    f0, p0, n = _PARITY.get(key, (0.0, 0.0, 0))
+    _PARITY[key] = (max(f0, float(floored)), max(p0, float(pure)), n + 1)
+
+
+@pytest.fixture(autouse=True)
+def _parity_scope(request):
+    _CURRENT[0] = request.node.nodeid.split("::", 1)[-1]
+    yield
+    _CURRENT[0] = None
+
+
+def pytest_terminal_summary(terminalreporter):
+    if not _PARITY:
+        return
+    tr = terminalreporter
+    tr.section("parity: max error per test, floored (asserted, <= 2e-3) | pure relative (reported)")
+    for key in sorted(_PARITY):
+        f, p, n = _PARITY[key]
+        tr.write_line(f"{f:9.3e} | {p:9.3e} | {n:3d} checks | {key}")
+    out = os.path.join(ROOT, "gpurun_out")
+    try:
+        os.makedirs(out, exist_ok=True)
+        import json
+        with open(os.path.join(out, "parity_errors.json"), "w") as fh:
+            json.dump({k: {"floored": v[0], "pure_relative": v[1], "checks": v[2]} for k, v in _PARITY.items()}, fh, indent=1)
+    except OSError:
+        pass
+
+
 def has_gpu() -> bool:
     try:
         import torch

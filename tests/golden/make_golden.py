@@ -1,8 +1,12 @@
-"""Generates tests/golden/dequant_from_*.npz from the reference's OWN numpy dequantiser.
+"""Generates tests/golden/*.npz by running the reference's OWN numpy code on seeded inputs.
 
 Run once in a checkout that has the reference project mounted:
 
     python tests/golden/make_golden.py /path/to/reference
+
+Two pieces of the reference can be executed without its GPU stack:
+
+dequant_from_*.npz
 
 `scripts/make-dsv2-layer-ref.py` cannot be imported (it parses argv at module scope), so
 the single function `dequant_from` (lines 102-116) is located with `ast`, compiled on
@@ -10,6 +14,13 @@ its own against numpy and executed on seeded inputs. Nothing of its source is st
 only the inputs and the outputs it produced. The reference documents that function as
 bit-identical to `mx.dequantize`, which makes these the only executed-reference vectors
 available for this path (the reference's WGSL and JS need WebGPU / node).
+
+kernel_ref_q{4,3}_*.npz
+`scripts/make-kernel-ref.py` builds its expected output inside `qwen36moe()`, a function that first imports mlx and
+opens a checkpoint (both absent here). The statements that follow (lines 55-66: the 4-bit nibble unpack / the 3-bit
+LSB-first bit-stream unpack, then `xg`, `dot`, `y` = sum_g s_g*dot_g + b_g*xsum_g) are pure numpy. They are
+located with `ast` inside that function (the `if bits == 4` statement and the assignments to xg, dot, y), compiled on
+their own and executed on seeded Wq / scales / biases / x. Stored: the inputs, the codes `nib` and `y` they produced.
 """
 import ast
 import os
@@ -30,10 +41,57 @@ def load_dequant_from(ref_root: str):
     return ns["dequant_from"]
 
 
+def load_kernel_ref_statements(ref_root: str):
+    """The unpack + factored-GEMV statements of qwen36moe() as a callable(ns) that executes them in `ns`."""
+    path = os.path.join(ref_root, "scripts", "make-kernel-ref.py")
+    tree = ast.parse(open(path).read())
+    fn = next(n for n in tree.body if isinstance(n, ast.FunctionDef) and n.name == "qwen36moe")
+    picked = []
+    for node in fn.body:
+        if isinstance(node, ast.If) and isinstance(node.test, ast.Compare) and getattr(node.test.left, "id", "") == "bits":
+            picked.append(node)                                   # if bits == 4: nibbles  else: bit stream
+        elif isinstance(node, ast.Assign) and len(node.targets) == 1 and getattr(node.targets[0], "id", "") in ("xg", "dot", "y"):
+            picked.append(node)
+    names = [getattr(n.targets[0], "id", None) if isinstance(n, ast.Assign) else "if" for n in picked]
+    assert names == ["if", "xg", "dot", "y"], names
+    code = compile(ast.Module(body=picked, type_ignores=[]), path, "exec")
+
+    def run(ns):
+        exec(code, ns)
+        return ns
+    return run
+
+
+def make_kernel_ref(ref_root: str):
+    run = load_kernel_ref_statements(ref_root)
+    cases = {
+        # name: (bits, N, K, seed, scale sigma)
+        "q4_small": (4, 24, 512, 21, 0.01), "q4_wide": (4, 48, 2048, 22, 0.01),
+        "q3_small": (3, 24, 512, 23, 0.02), "q3_wide": (3, 48, 4096, 24, 0.02), "q3_ragged": (3, 13, 1408, 25, 0.02),
+    }
+    G = 64
+    for name, (bits, N, K, seed, sig) in cases.items():
+        rng = np.random.default_rng(seed)
+        Wq = rng.integers(0, 1 << 32, size=(N, K * bits // 32), dtype=np.uint64).astype(np.uint32)
+        S = np.abs(rng.standard_normal((N, K // G), dtype=np.float32) * np.float32(sig))
+        B = rng.standard_normal((N, K // G), dtype=np.float32) * np.float32(0.05)
+        x = (rng.standard_normal(K) * 0.05).astype(np.float16)     # the reference's activation scale (line 53)
+        ns = {"np": np, "bits": bits, "Wq": Wq, "N": N, "K": K, "NG": K // G, "G": G, "x_f16": x,
+              "scales_f16": S.astype(np.float16), "bias_f16": B.astype(np.float16)}
+        run(ns)
+        nib, y = ns["nib"], ns["y"]
+        assert nib.shape == (N, K) and nib.max() < (1 << bits) and y.shape == (N,)
+        np.savez_compressed(os.path.join(HERE, f"kernel_ref_{name}.npz"), W=Wq, scales=ns["scales_f16"],
+                            biases=ns["bias_f16"], x=x, codes=nib.astype(np.uint8), y=y.astype(np.float32),
+                            bits=np.int32(bits))
+        print(name, Wq.shape, "-> codes", nib.shape, "y", y.shape)
+
+
 def main():
     if len(sys.argv) < 2:
         raise SystemExit("usage: make_golden.py <path to a checkout of the reference project>")
     ref_root = sys.argv[1]
+    make_kernel_ref(ref_root)
     dequant_from = load_dequant_from(ref_root)
     cases = {
         # name: (N, K, seed, scale sigma, extreme)

@@ -7,6 +7,7 @@ import pytest
 
 import zero_tvm_b200 as z
 from oracle import ztvm_oracle as zo
+from conftest import record_parity
 from zero_tvm_b200.backend import pick_chunk_gemm, pod_args
 
 pytestmark = pytest.mark.gpu
@@ -35,6 +36,7 @@ def check(y, p, oracle_c):
     y64 = oracle_c.matmul_f64(p["x"], p["W"], p["scales"], p["biases"], p["group"], 4, p["affine"], w16=True)
     assert np.isfinite(y).all()
     err = zo.rel_err_scaled(y, y64, FLOOR_FRAC)
+    record_parity(err, zo.rel_err(y, y64))     # floored and pure-relative error, listed at the end of the run
     assert err <= TOL, f"rel err {err:.3e} (floor 1e-3 rms: {zo.rel_err_scaled(y, y64):.3e})"
     return err
 

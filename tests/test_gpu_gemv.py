@@ -11,6 +11,7 @@ import pytest
 import zero_tvm_b200 as z
 from oracle import ztvm_oracle as zo
 from zero_tvm_b200.backend import pod_args, resolve_matmul
+from conftest import record_parity
 
 pytestmark = pytest.mark.gpu
 TOL = 2e-3       # the path's stated tolerance, graded with oracle.rel_err_scaled (floor = 1e-3 of the output rms)
@@ -40,6 +41,7 @@ def check_y(y, p, oracle_c, w16=None, tol=TOL):
     assert np.isfinite(y).all(), "output holds NaN/inf (poison not overwritten?)"
     assert np.abs(y).max() > 0
     err = zo.rel_err_scaled(y, y64, 1e-2 if w16 else 1e-3)
+    record_parity(err, zo.rel_err(y, y64))     # floored and pure-relative error, listed at the end of the run
     assert err <= tol, f"rel err {err:.3e} (pure relative {zo.rel_err(y, y64):.3e})"
     return err
 
@@ -74,12 +76,37 @@ def test_codes_and_dequant_bit_exact(bits, group, affine, N, K, backend, dev, or
     codes = dev.empty((N, K), np.uint8, fill=255)
     backend.ctx.unpack_codes(d, codes, W)
     assert np.array_equal(dev.get(codes), p["q"])
+    # the in-place subnormal codes the streaming matrix-unit kernels multiply with (their own mask functions)
+    codes_s = dev.empty((N, K), np.uint8, fill=255)
+    backend.ctx.unpack_codes_streamed(d, codes_s, W)
+    assert np.array_equal(dev.get(codes_s), p["q"])
     for as_f16 in (False, True):
         out = dev.empty((N, K), np.float16 if as_f16 else np.float32)
         backend.ctx.dequant(d, out, as_f16, s, W, b)
         ref = oracle_c.dequant(p["W"], p["scales"], p["biases"], group, bits, affine, out_f16=as_f16)
         got = dev.get(out)
         assert np.array_equal(got.view(np.uint16 if as_f16 else np.uint32), ref.view(np.uint16 if as_f16 else np.uint32))
+
+
+@pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(GOLDEN, "kernel_ref_*.npz"))))
+def test_kernel_ref_vectors(path, backend, dev):
+    """Vectors produced by the reference's own numpy statements (scripts/make-kernel-ref.py:55-66): both code hooks
+    bit-exact against its unpack (4-bit nibbles, 3-bit bit stream), the GEMV within 2e-3 of its factored y."""
+    g = np.load(path)
+    bits = int(g["bits"])
+    N, K = g["codes"].shape
+    d = z.MmDesc(K, N, 1, 64, bits, 1, 0)
+    W = dev.put(g["W"])
+    for hook in (backend.ctx.unpack_codes, backend.ctx.unpack_codes_streamed):
+        codes = dev.empty((N, K), np.uint8, fill=255)
+        hook(d, codes, W)
+        assert np.array_equal(dev.get(codes), g["codes"]), hook.__name__
+    p = dict(x=g["x"].reshape(1, K), W=g["W"], scales=g["scales"], biases=g["biases"], N=N, K=K, M=1, bits=bits,
+             group=64, affine=True)
+    y = run_matmul(backend, dev, p, out_f32=True)[0]
+    err = zo.rel_err_scaled(y, g["y"], 1e-3)
+    record_parity(err, zo.rel_err(y, g["y"]))
+    assert err <= TOL, f"rel err {err:.3e} against the reference's factored y"
 
 
 # ---- the reference's own kernel tests ----------------------------------------------------------------

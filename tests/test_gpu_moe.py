@@ -5,6 +5,7 @@ import pytest
 
 import zero_tvm_b200 as z
 from oracle import ztvm_oracle as zo
+from conftest import record_parity
 from zero_tvm_b200.backend import moe_down_pod_args, moe_gate_pod_args, resolve_matmul
 
 pytestmark = pytest.mark.gpu
@@ -67,14 +68,18 @@ def check_block(got, mb, oracle_c, K_top=8, bits=4, pairs_run=None):
         tiles = moe_kernel_kind(pairs_run or ids_ref.size, experts, K, N, bits) == "tiles"
         ref = oracle_c.moe_matmul_f64(x_in, *mb[proj], ids_ref, N, K, 64, bits, in_per_slot=per_slot, w16=tiles)
         return ref, (1e-2 if tiles else 1e-3)
+    def graded(y, ref, frac=1e-3):
+        err = zo.rel_err_scaled(y, ref, frac)
+        record_parity(err, zo.rel_err(y, ref))
+        return err
     g64, fr = anchor(mb["x"], "gate", ffn, d, False)
-    assert zo.rel_err_scaled(got["gate_up"][..., :ffn], g64, fr) <= TOL
+    assert graded(got["gate_up"][..., :ffn], g64, fr) <= TOL
     u64, fr = anchor(mb["x"], "up", ffn, d, False)
-    assert zo.rel_err_scaled(got["gate_up"][..., ffn:], u64, fr) <= TOL
+    assert graded(got["gate_up"][..., ffn:], u64, fr) <= TOL
     h_ref = oracle_c.silu_mul(got["gate_up"], ffn)
-    assert zo.rel_err_scaled(got["h"], h_ref.astype(np.float64)) <= TOL
+    assert graded(got["h"], h_ref.astype(np.float64)) <= TOL
     d64, fr = anchor(got["h"], "down", d, ffn, True)
-    assert zo.rel_err_scaled(got["y_slots"], d64, fr) <= TOL
+    assert graded(got["y_slots"], d64, fr) <= TOL
     y_ref = oracle_c.moe_combine(got["y_slots"], got["scores"])
     assert np.array_equal(got["y"].view(np.uint16), y_ref.view(np.uint16))
     assert np.isfinite(got["y"].astype(np.float32)).all()

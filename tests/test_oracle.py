@@ -32,6 +32,30 @@ def test_dequant_matches_reference_dequant_from(path, oracle_c):
 
 def test_golden_files_present():
     assert len(glob.glob(os.path.join(GOLDEN, "dequant_from_*.npz"))) >= 4
+    assert len(glob.glob(os.path.join(GOLDEN, "kernel_ref_q3_*.npz"))) >= 3
+    assert len(glob.glob(os.path.join(GOLDEN, "kernel_ref_q4_*.npz"))) >= 2
+
+
+@pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(GOLDEN, "kernel_ref_*.npz"))))
+def test_unpack_and_factored_gemv_match_reference_kernel_ref(path, oracle_c):
+    """Codes must equal, bit for bit, what the unpack statements of scripts/make-kernel-ref.py:55-63 produced (4-bit
+    nibbles, 3-bit LSB-first bit stream); y must sit within 2e-3 of its factored reference
+    y = sum_g s_g*dot_g + b_g*xsum_g (lines 64-66), for the f64 anchor and for the reference-order f32 GEMV."""
+    g = np.load(path)
+    bits = int(g["bits"])
+    assert np.array_equal(zo.unpack_codes(g["W"], bits), g["codes"])
+    assert np.array_equal(oracle_c.unpack_codes(g["W"], bits), g["codes"])
+    if bits == 3:
+        assert np.array_equal(zo.unpack_codes_q3_window(g["W"]), g["codes"])
+    assert np.array_equal(zo.pack_codes(g["codes"], bits), g["W"])
+    x = g["x"].reshape(1, -1)
+    w32 = zo.dequant_w32(g["codes"], g["scales"], g["biases"], 64)
+    y64 = zo.matmul_f64(x, w32)[0]
+    assert zo.rel_err_scaled(g["y"], y64, 1e-3) <= 2e-3
+    for got in (zo.gemv_word_order_f32(x, g["W"], g["scales"], g["biases"], 64, bits)[0],
+                oracle_c.gemv_ref(x, g["W"], g["scales"], g["biases"], 64, bits, True, out_f32=True)[0],
+                oracle_c.matmul_f64(x, g["W"], g["scales"], g["biases"], 64, bits)[0]):
+        assert zo.rel_err_scaled(got, g["y"], 1e-3) <= 2e-3
 
 
 @pytest.mark.parametrize("bits", [4, 3])

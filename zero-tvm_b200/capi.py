@@ -16,7 +16,7 @@ SYMBOLS = [
     "ztvm_version", "ztvm_status_string", "ztvm_init", "ztvm_destroy", "ztvm_last_error", "ztvm_sync",
     "ztvm_int4_matmul", "ztvm_int4_matmul_multi", "ztvm_int4_matmul_host", "ztvm_int4_matmul_moe", "ztvm_int4_matmul_moe_noalloc",
     "ztvm_moe_route_topk", "ztvm_moe_dispatch_plan", "ztvm_silu_mul",
-    "ztvm_moe_combine", "ztvm_unpack_codes", "ztvm_dequant", "ztvm_device_errors",
+    "ztvm_moe_combine", "ztvm_unpack_codes", "ztvm_unpack_codes_streamed", "ztvm_dequant", "ztvm_device_errors",
 ]
 
 OK, ERR_NULL_POINTER, ERR_BAD_DIMS, ERR_UNSUPPORTED, ERR_ALIGNMENT, ERR_CUDA, ERR_BAD_CONTEXT, ERR_TOO_LARGE = range(8)
@@ -70,6 +70,7 @@ def load() -> C.CDLL:
         "ztvm_silu_mul": [vp, u32, u32, vp, vp, vp],
         "ztvm_moe_combine": [vp, u32, u32, u32, vp, vp, vp, vp],
         "ztvm_unpack_codes": [vp, C.POINTER(MmDesc), vp, vp, vp],
+        "ztvm_unpack_codes_streamed": [vp, C.POINTER(MmDesc), vp, vp, vp],
         "ztvm_dequant": [vp, C.POINTER(MmDesc), vp, i32, vp, vp, vp, vp],
         "ztvm_device_errors": [vp, vp, C.POINTER(u32)],
     }
@@ -174,6 +175,10 @@ class Context:
 
     def unpack_codes(self, desc: MmDesc, codes, packed_w, stream=None):
         check(self._lib.ztvm_unpack_codes(self.handle, C.byref(desc), ptr(codes), ptr(packed_w), stream_ptr(stream)))
+
+    def unpack_codes_streamed(self, desc: MmDesc, codes, packed_w, stream=None):
+        """Codes as the streaming matrix-unit kernels consume them (in-place f16 subnormals scaled back to integers)."""
+        check(self._lib.ztvm_unpack_codes_streamed(self.handle, C.byref(desc), ptr(codes), ptr(packed_w), stream_ptr(stream)))
 
     def dequant(self, desc: MmDesc, w_out, as_f16, scales, packed_w, biases=None, stream=None):
         check(self._lib.ztvm_dequant(self.handle, C.byref(desc), ptr(w_out), int(as_f16), ptr(scales),

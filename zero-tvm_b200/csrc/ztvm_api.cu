@@ -519,6 +519,19 @@ ztvm_status ztvm_unpack_codes(ztvm_ctx* ctx, const ztvm_mm_desc* d, uint8_t* cod
   return ZTVM_OK;
 }
 
+ztvm_status ztvm_unpack_codes_streamed(ztvm_ctx* ctx, const ztvm_mm_desc* d, uint8_t* codes, const void* packed_w,
+                                       void* stream) {
+  ztvm_status s = check_ctx(ctx);
+  if (s) return s;
+  if ((s = check_desc(d, false))) return s;
+  if (!codes || !packed_w) return fail(ZTVM_ERR_NULL_POINTER, "codes/packed_w must be non-NULL");
+  if (!aligned(codes, 8) || !aligned(packed_w, 4)) return fail(ZTVM_ERR_ALIGNMENT, "codes need 8-byte alignment");
+  if (d->bits == 3 && d->K % 64) return fail(ZTVM_ERR_BAD_DIMS, "3-bit streams are unpacked per 64 codes: K=%u", d->K);
+  cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : ctx->stream;
+  ZTVM_CUDA(ztvm::launch_unpack_codes_streamed(static_cast<const uint32_t*>(packed_w), codes, d->N, d->K, (int)d->bits, st));
+  return ZTVM_OK;
+}
+
 ztvm_status ztvm_dequant(ztvm_ctx* ctx, const ztvm_mm_desc* d, void* w_out, int32_t as_f16, const void* scales,
                          const void* packed_w, const void* biases, void* stream) {
   ztvm_status s = check_ctx(ctx);

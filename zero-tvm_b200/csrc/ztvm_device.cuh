@@ -58,6 +58,26 @@ __device__ __forceinline__ Codes8 unpack4(uint32_t w) {
   c.p37 = __hsub2(u32_as_h2(lop3_and_or(w8, 0x00F000F0u, 0x54005400u)), k64);
   return c;
 }
+// The same eight codes WITHOUT any arithmetic: a nibble masked where it sits is already an f16 subnormal,
+// (w & 0x000F) = q * 2^-24 and (w & 0x00F0) = q * 2^-20 in each 16-bit half. The four registers hold the pairs
+// (q0,q4) * 2^-24, (q1,q5) * 2^-20, (q2,q6) * 2^-24, (q3,q7) * 2^-20. Every streaming kernel (the persistent GEMV, the
+// tiled GEMVs, the streaming grouped MoE kernel) feeds its multiplier array with exactly these registers, and the
+// parity hook ztvm_unpack_codes_streamed turns them back into integers.
+struct Inplace4 {
+  uint32_t lo04, hi15, lo26, hi37;
+};
+__device__ __forceinline__ Inplace4 codes4_inplace(uint32_t w) {
+  const uint32_t w8 = w >> 8;
+  Inplace4 c;
+  c.lo04 = w & 0x000F000Fu;
+  c.hi15 = w & 0x00F000F0u;
+  c.lo26 = w8 & 0x000F000Fu;
+  c.hi37 = w8 & 0x00F000F0u;
+  return c;
+}
+constexpr float kInplaceLoScale = 16777216.f;   // 2^24: subnormal of the low-nibble mask -> integer code
+constexpr float kInplaceHiScale = 1048576.f;    // 2^20: subnormal of the high-nibble mask -> integer code
+
 // The eight codes as f32, in natural order q[0..7].
 __device__ __forceinline__ void codes4_f32(uint32_t w, float q[8]) {
   Codes8 c = unpack4(w);
@@ -81,6 +101,27 @@ __device__ __forceinline__ uint32_t window3(uint32_t w0, uint32_t w1, uint32_t w
 __device__ __forceinline__ void codes3_f32(uint32_t win, float q[8]) {
 #pragma unroll
   for (int i = 0; i < 8; ++i) q[i] = (float)((win >> (3 * i)) & 7u);
+}
+
+// In-place 3-bit codes for the matrix unit. `w` holds one scale group of a row: 64 codes = 192 bits = six words.
+// A 3-bit code anywhere in bits 0..9 of a 16-bit half is an f16 subnormal q * 2^(o-24) (o = its bit offset in the half).
+// View k (0..16) is the 32-bit window of the stream that starts on code c = codes3_view_first(k): its low half holds
+// codes c, c+1 at offsets 0, 3 and its high half codes c+6, c+7 at offsets 2, 5, so two ANDs give
+//   r0 = (code c | code c+6)   with values q * 2^-24 | q * 2^-22
+//   r1 = (code c+1 | code c+7) with values q * 2^-21 | q * 2^-19
+// Views 0..14 tile codes 0..59 in pairs (c = 12 (k/3) + 2 (k%3)); views 15, 16 cover codes 60..63 with their low half
+// only. The powers of two are moved onto the activations by the kernel that multiplies.
+__host__ __device__ constexpr int codes3_view_first(int k) { return k < 15 ? 12 * (k / 3) + 2 * (k % 3) : 60 + 2 * (k - 15); }
+constexpr int kCodes3Views = 17;
+__device__ __forceinline__ void codes3_inplace(const uint32_t (&w)[6], int k, uint32_t& r0, uint32_t& r1) {
+  constexpr uint32_t kM0 = 0x001C0007u, kM1 = 0x00E00038u;
+  const int bit = 3 * codes3_view_first(k), j = bit >> 5, sh = bit & 31;
+  uint32_t v;
+  if (sh == 0) v = w[j];
+  else if (sh <= 8 || j == 5) v = w[j] >> sh;             // the window fits in one word
+  else v = __funnelshift_r(w[j], w[j + 1 < 6 ? j + 1 : 5], sh);
+  r0 = v & (k < 15 ? kM0 : (kM0 & 0xFFFFu));
+  r1 = v & (k < 15 ? kM1 : (kM1 & 0xFFFFu));
 }
 
 // ---- canonical dequantisers ----------------------------------------------------------------

@@ -309,8 +309,8 @@ gemv_fma_m1_kernel(const GemvParams p) {
 #pragma unroll
       for (int r = 0; r < ROWS; ++r) {
         const uint32_t w = j == 0 ? wcur[r].x : j == 1 ? wcur[r].y : j == 2 ? wcur[r].z : wcur[r].w;
-        const uint32_t w8 = w >> 8;
-        const uint32_t a0 = w & 0x000F000Fu, a1 = w & 0x00F000F0u, a2 = w8 & 0x000F000Fu, a3 = w8 & 0x00F000F0u;
+        const Inplace4 ip = codes4_inplace(w);
+        const uint32_t a0 = ip.lo04, a1 = ip.hi15, a2 = ip.lo26, a3 = ip.hi37;
         float lo = dlo[r], hi = dhi[r];
         lo = fma_f16_lo(xp.x, a0, lo); lo = fma_f16_hi(xp.x, a0, lo);   // x0*q0, x4*q4
         hi = fma_f16_lo(xp.y, a1, hi); hi = fma_f16_hi(xp.y, a1, hi);   // x1*q1, x5*q5
@@ -497,8 +497,8 @@ gemv_fma_m1_persist_kernel(const GemvParams p) {
 #pragma unroll
           for (int r = 0; r < ROWS; ++r) {
             const uint32_t w = j == 0 ? wv[r].x : j == 1 ? wv[r].y : j == 2 ? wv[r].z : wv[r].w;
-            const uint32_t w8 = w >> 8;
-            const uint32_t a0 = w & 0x000F000Fu, a1 = w & 0x00F000F0u, a2 = w8 & 0x000F000Fu, a3 = w8 & 0x00F000F0u;
+            const Inplace4 ip = codes4_inplace(w);
+            const uint32_t a0 = ip.lo04, a1 = ip.hi15, a2 = ip.lo26, a3 = ip.hi37;
             float lo = dlo[r], hi = dhi[r];
             lo = fma_f16_lo(xp.x, a0, lo); lo = fma_f16_hi(xp.x, a0, lo);
             hi = fma_f16_lo(xp.y, a1, hi); hi = fma_f16_hi(xp.y, a1, hi);

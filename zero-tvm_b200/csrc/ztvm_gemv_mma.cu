@@ -222,13 +222,13 @@ gemv_mma_kernel(const GemvParams p) {
           uint4 xb = make_uint4(0u, 0u, 0u, 0u);
           if (g < NTOK) xb = smem_u4[xitem<WPL, NTOK>(gb + i, t, g, c)];
           const uint32_t wg = qa[i].w[t], wh = qb[i].w[t];
-          const uint32_t ug = wg >> 8, uh = wh >> 8;
+          const Inplace4 cg = codes4_inplace(wg), ch = codes4_inplace(wh);
           if (t == 0) {
-            mma_16816(clo, wg & 0x000F000Fu, wh & 0x000F000Fu, ug & 0x000F000Fu, uh & 0x000F000Fu, xb.x, xb.y, kZero);
-            mma_16816(chi, wg & 0x00F000F0u, wh & 0x00F000F0u, ug & 0x00F000F0u, uh & 0x00F000F0u, xb.z, xb.w, kZero);
+            mma_16816(clo, cg.lo04, ch.lo04, cg.lo26, ch.lo26, xb.x, xb.y, kZero);
+            mma_16816(chi, cg.hi15, ch.hi15, cg.hi37, ch.hi37, xb.z, xb.w, kZero);
           } else {
-            mma_16816(clo, wg & 0x000F000Fu, wh & 0x000F000Fu, ug & 0x000F000Fu, uh & 0x000F000Fu, xb.x, xb.y, clo);
-            mma_16816(chi, wg & 0x00F000F0u, wh & 0x00F000F0u, ug & 0x00F000F0u, uh & 0x00F000F0u, xb.z, xb.w, chi);
+            mma_16816(clo, cg.lo04, ch.lo04, cg.lo26, ch.lo26, xb.x, xb.y, clo);
+            mma_16816(chi, cg.hi15, ch.hi15, cg.hi37, ch.hi37, xb.z, xb.w, chi);
           }
         }
         // fold the group: acc += s*(2^24*lo + 2^20*hi) + b*xsum

@@ -27,11 +27,11 @@ constexpr int kT3TileW = 16 * kT3RowBytes;               // 1536
 constexpr int kT3TileBytes = kT3TileW + 16 * 16;         // + per row 4 scales, 4 biases (f16)
 constexpr int kT3RingBytes = kTcWarps * kTcDepth * kT3TileBytes;
 constexpr int kT3Rounds = 4;
-constexpr int kT3Views = 17;
+constexpr int kT3Views = kCodes3Views;
 constexpr uint32_t kT3MaxAccBytes = 32 * 1024;
 
-// first code of window k inside the lane's group
-__host__ __device__ constexpr int t3_code(int k) { return k < 15 ? 12 * (k / 3) + 2 * (k % 3) : 60 + 2 * (k - 15); }
+// first code of window k inside the lane's group (the unpack itself is codes3_inplace, shared with the parity hook)
+__host__ __device__ constexpr int t3_code(int k) { return codes3_view_first(k); }
 
 __global__ void __launch_bounds__(kTcWarps * 32, 1)
 gemv_tc3_kernel(const GemvParams p) {   // 3-bit weights exist only in the affine layout
@@ -158,17 +158,13 @@ gemv_tc3_kernel(const GemvParams p) {   // 3-bit weights exist only in the affin
           float d0[4], d1[4];   // two accumulation chains
 #pragma unroll
           for (int k = 0; k < kT3Views; ++k) {
-            constexpr uint32_t kM0 = 0x001C0007u, kM1 = 0x00E00038u;
-            const int bit = 3 * t3_code(k), j = bit >> 5, sh = bit & 31;
-            uint32_t vw, vu;
-            if (sh == 0) { vw = w[j]; vu = u[j]; }
-            else if (sh <= 8 || j == 5) { vw = w[j] >> sh; vu = u[j] >> sh; }           // the window fits in one word
-            else { vw = __funnelshift_r(w[j], w[j + 1], sh); vu = __funnelshift_r(u[j], u[j + 1], sh); }
-            const uint32_t m0 = k < 15 ? kM0 : (kM0 & 0xFFFFu), m1 = k < 15 ? kM1 : (kM1 & 0xFFFFu);
-            if (k == 0) tc_mma(d0, vw & m0, vu & m0, vw & m1, vu & m1, xb[k][0], xb[k][1], kZero);
-            else if (k == 1) tc_mma(d1, vw & m0, vu & m0, vw & m1, vu & m1, xb[k][0], xb[k][1], kZero);
-            else if (k & 1) tc_mma(d1, vw & m0, vu & m0, vw & m1, vu & m1, xb[k][0], xb[k][1], d1);
-            else tc_mma(d0, vw & m0, vu & m0, vw & m1, vu & m1, xb[k][0], xb[k][1], d0);
+            uint32_t w0, w1, u0, u1;
+            codes3_inplace(w, k, w0, w1);
+            codes3_inplace(u, k, u0, u1);
+            if (k == 0) tc_mma(d0, w0, u0, w1, u1, xb[k][0], xb[k][1], kZero);
+            else if (k == 1) tc_mma(d1, w0, u0, w1, u1, xb[k][0], xb[k][1], kZero);
+            else if (k & 1) tc_mma(d1, w0, u0, w1, u1, xb[k][0], xb[k][1], d1);
+            else tc_mma(d0, w0, u0, w1, u1, xb[k][0], xb[k][1], d0);
           }
           // fold: columns 2c, 2c + 1 of the accumulator are groups 2c, 2c + 1 (lanes with c >= 2 hold empty columns)
 #pragma unroll

@@ -2,6 +2,7 @@
 // router top-k, SiLU*up, weighted combine.
 #include "ztvm_device.cuh"
 #include "ztvm_kernels.h"
+#include "ztvm_tc.cuh"
 
 namespace ztvm {
 
@@ -49,9 +50,18 @@ __global__ void dequant_kernel(const uint32_t* W, const __half* S, const __half*
   const size_t total = (size_t)N * nblk;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const uint32_t n = (uint32_t)(i / nblk), blk = (uint32_t)(i - (size_t)n * nblk);
+    const uint32_t g = (blk << 3) >> group_shift;
+    if constexpr (AS_F16 && BITS == 4) {
+      // the tensor-core GEMMs (dense and grouped) build their f16 operand with dequant_word_w16: so does the hook
+      const unsigned short s16 = reinterpret_cast<const unsigned short*>(S)[(size_t)n * SPR + g];
+      const unsigned short b16 = AFFINE ? reinterpret_cast<const unsigned short*>(B)[(size_t)n * SPR + g] : (unsigned short)0;
+      const uint4 v = dequant_word_w16<AFFINE>(W[(size_t)n * KP + blk], s16, __half2float(__ushort_as_half(s16)),
+                                               __half2float(__ushort_as_half(b16)));
+      *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(out) + i * 8) = v;
+      continue;
+    }
     float q[8];
     load_block_codes<BITS>(W, KP, n, blk, q);
-    const uint32_t g = (blk << 3) >> group_shift;
     const float s = __half2float(S[(size_t)n * SPR + g]);
     const float b = AFFINE ? __half2float(B[(size_t)n * SPR + g]) : 0.f;
     if constexpr (AS_F16) {
@@ -71,6 +81,54 @@ __global__ void dequant_kernel(const uint32_t* W, const __half* S, const __half*
   }
 }
 
+// The codes as the streaming kernels see them: in-place masks that are f16 subnormals (codes4_inplace / codes3_inplace,
+// the functions those kernels call), scaled back to integers. 4-bit: one thread per word. 3-bit: one thread per
+// (row, scale group of 64 codes = six words), the unit a lane of the 3-bit GEMV owns.
+__device__ __forceinline__ uint32_t sub_to_code(uint32_t halfbits, float scale) {
+  return (uint32_t)(__half2float(__ushort_as_half((unsigned short)halfbits)) * scale);
+}
+template <int BITS>
+__global__ void unpack_codes_streamed_kernel(const uint32_t* W, uint8_t* codes, uint32_t N, uint32_t K) {
+  if constexpr (BITS == 4) {
+    const uint32_t KP = K >> 3;
+    const size_t total = (size_t)N * KP;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+      const Inplace4 c = codes4_inplace(W[i]);
+      uint32_t q[8];
+      q[0] = sub_to_code(c.lo04 & 0xFFFFu, kInplaceLoScale); q[4] = sub_to_code(c.lo04 >> 16, kInplaceLoScale);
+      q[1] = sub_to_code(c.hi15 & 0xFFFFu, kInplaceHiScale); q[5] = sub_to_code(c.hi15 >> 16, kInplaceHiScale);
+      q[2] = sub_to_code(c.lo26 & 0xFFFFu, kInplaceLoScale); q[6] = sub_to_code(c.lo26 >> 16, kInplaceLoScale);
+      q[3] = sub_to_code(c.hi37 & 0xFFFFu, kInplaceHiScale); q[7] = sub_to_code(c.hi37 >> 16, kInplaceHiScale);
+      uint2 o;
+      o.x = q[0] | (q[1] << 8) | (q[2] << 16) | (q[3] << 24);
+      o.y = q[4] | (q[5] << 8) | (q[6] << 16) | (q[7] << 24);
+      *reinterpret_cast<uint2*>(codes + i * 8) = o;
+    }
+  } else {
+    const uint32_t groups = K >> 6, KP = K / 32 * 3;
+    const size_t total = (size_t)N * groups;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+      const uint32_t n = (uint32_t)(i / groups), g = (uint32_t)(i - (size_t)n * groups);
+      uint32_t w[6];
+#pragma unroll
+      for (int j = 0; j < 6; ++j) w[j] = W[(size_t)n * KP + g * 6 + j];
+      uint8_t* dst = codes + (size_t)n * K + (size_t)g * 64;
+#pragma unroll
+      for (int k = 0; k < kCodes3Views; ++k) {
+        uint32_t r0, r1;
+        codes3_inplace(w, k, r0, r1);
+        const int c0 = codes3_view_first(k);
+        dst[c0] = (uint8_t)sub_to_code(r0 & 0xFFFFu, 16777216.f);            // offset 0: q * 2^-24
+        dst[c0 + 1] = (uint8_t)sub_to_code(r1 & 0xFFFFu, 2097152.f);         // offset 3: q * 2^-21
+        if (k < 15) {
+          dst[c0 + 6] = (uint8_t)sub_to_code(r0 >> 16, 4194304.f);           // offset 2: q * 2^-22
+          dst[c0 + 7] = (uint8_t)sub_to_code(r1 >> 16, 524288.f);            // offset 5: q * 2^-19
+        }
+      }
+    }
+  }
+}
+
 static inline unsigned grid_for(size_t total, int block) {
   size_t g = (total + block - 1) / block;
   return (unsigned)(g > 148 * 32 ? 148 * 32 : (g ? g : 1));
@@ -80,6 +138,12 @@ cudaError_t launch_unpack_codes(const uint32_t* W, uint8_t* codes, uint32_t N, u
   const size_t total = (size_t)N * (K >> 3);
   if (bits == 4) unpack_codes_kernel<4><<<grid_for(total, 256), 256, 0, st>>>(W, codes, N, K);
   else unpack_codes_kernel<3><<<grid_for(total, 256), 256, 0, st>>>(W, codes, N, K);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_unpack_codes_streamed(const uint32_t* W, uint8_t* codes, uint32_t N, uint32_t K, int bits, cudaStream_t st) {
+  if (bits == 4) unpack_codes_streamed_kernel<4><<<grid_for((size_t)N * (K >> 3), 256), 256, 0, st>>>(W, codes, N, K);
+  else unpack_codes_streamed_kernel<3><<<grid_for((size_t)N * (K >> 6), 256), 256, 0, st>>>(W, codes, N, K);
   return cudaGetLastError();
 }
 

@@ -78,6 +78,8 @@ cudaError_t launch_gemm_w4_ta(const uint32_t* W, const __half* S, const __half* 
                               uint32_t N, uint32_t K, uint32_t group_shift, bool out_f32, uint32_t* status, cudaStream_t st);
 
 cudaError_t launch_unpack_codes(const uint32_t* W, uint8_t* codes, uint32_t N, uint32_t K, int bits, cudaStream_t st);
+// The codes as the streaming matrix-unit kernels consume them (in-place f16 subnormals, scaled back to integers).
+cudaError_t launch_unpack_codes_streamed(const uint32_t* W, uint8_t* codes, uint32_t N, uint32_t K, int bits, cudaStream_t st);
 cudaError_t launch_dequant(const uint32_t* W, const __half* S, const __half* B, void* out, uint32_t N, uint32_t K,
                            int bits, uint32_t group_shift, bool affine, bool as_f16, cudaStream_t st);
 

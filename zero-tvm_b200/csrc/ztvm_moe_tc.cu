@@ -142,14 +142,14 @@ moe_tc_kernel(const MoeTcParams p) {
           const uint2 wg = tc_lds64(st + (uint32_t)g * 128 + off), wh = tc_lds64(st + (uint32_t)(g + 8) * 128 + off);
           float clo[4], chi[4];
           {
-            const uint32_t ug = wg.x >> 8, uh = wh.x >> 8;
-            tc_mma(clo, wg.x & 0x000F000Fu, wh.x & 0x000F000Fu, ug & 0x000F000Fu, uh & 0x000F000Fu, xf[tq][0][0], xf[tq][0][1], kZero);
-            tc_mma(chi, wg.x & 0x00F000F0u, wh.x & 0x00F000F0u, ug & 0x00F000F0u, uh & 0x00F000F0u, xf[tq][0][2], xf[tq][0][3], kZero);
+            const Inplace4 cg = codes4_inplace(wg.x), ch = codes4_inplace(wh.x);   // rows g and g + 8
+            tc_mma(clo, cg.lo04, ch.lo04, cg.lo26, ch.lo26, xf[tq][0][0], xf[tq][0][1], kZero);
+            tc_mma(chi, cg.hi15, ch.hi15, cg.hi37, ch.hi37, xf[tq][0][2], xf[tq][0][3], kZero);
           }
           {
-            const uint32_t ug = wg.y >> 8, uh = wh.y >> 8;
-            tc_mma(clo, wg.y & 0x000F000Fu, wh.y & 0x000F000Fu, ug & 0x000F000Fu, uh & 0x000F000Fu, xf[tq][1][0], xf[tq][1][1], clo);
-            tc_mma(chi, wg.y & 0x00F000F0u, wh.y & 0x00F000F0u, ug & 0x00F000F0u, uh & 0x00F000F0u, xf[tq][1][2], xf[tq][1][3], chi);
+            const Inplace4 cg = codes4_inplace(wg.y), ch = codes4_inplace(wh.y);
+            tc_mma(clo, cg.lo04, ch.lo04, cg.lo26, ch.lo26, xf[tq][1][0], xf[tq][1][1], clo);
+            tc_mma(chi, cg.hi15, ch.hi15, cg.hi37, ch.hi37, xf[tq][1][2], xf[tq][1][3], chi);
           }
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
