@@ -49,6 +49,18 @@ class OracleKernels:
         self.zc.moe_gemv_ref(h, *st(down), ids, d, ffn, 64, 4, ffn, d, ffn, d, out.reshape(-1))
         y_rows.copy_(torch.from_numpy(out))
 
+    def block_ffn(self, y_slots, gu, h, x, ids, gate, up, down, d, ffn, tokens, slots):
+        """One rank: gate, up, SiLU, down over the id list [tokens, slots] (x shared by the slots of a token)."""
+        idn = self._np(ids).astype(np.uint32)
+        st = lambda t3: (self._np(t3[0], np.uint32), self._np(t3[1]), self._np(t3[2]))
+        g = np.zeros((tokens, slots, 2 * ffn), dtype=np.float16)
+        self.zc.moe_gemv_ref(self._np(x), *st(gate), idn, ffn, d, 64, 4, 0, 2 * ffn, d, slots * 2 * ffn, g.reshape(-1))
+        self.zc.moe_gemv_ref(self._np(x), *st(up), idn, ffn, d, 64, 4, 0, 2 * ffn, d, slots * 2 * ffn, g.reshape(-1)[ffn:])
+        hh = self.zc.silu_mul(g.reshape(tokens * slots, 2 * ffn), ffn).reshape(tokens, slots, ffn)
+        out = np.zeros((tokens, slots, d), dtype=np.float16)
+        self.zc.moe_gemv_ref(hh, *st(down), idn, d, ffn, 64, 4, ffn, d, slots * ffn, slots * d, out.reshape(-1))
+        y_slots.copy_(torch.from_numpy(out))
+
     def dense_ffn(self, x, gate, up, down, e, d, ffn, rows):
         y = torch.empty((rows, d), dtype=torch.float16)
         self.expert_ffn(y, x, torch.full((rows, 1), e, dtype=torch.int32), gate, up, down, d, ffn, rows)

@@ -91,6 +91,18 @@ class CudaKernels:
         self.be.dispatch(ent_d, [y_rows, h, down[1], down[0], moe_down_pod_args(d, ffn, 1), down[2], local_ids],
                          (d // 4, rows, 1), stream=st)
 
+    def block_ffn(self, y_slots, gu, h, x, ids, gate, up, down, d, ffn, tokens, slots):
+        """The engine's own sequence over an id list [tokens, slots]: gate and up into the halves of gu, SiLU, down."""
+        st = self._stream()
+        ent_g = resolve_matmul(affine=True, K=d, moe=True)
+        ent_d = resolve_matmul(affine=True, K=ffn, moe=True)
+        grid = (ffn // 4, tokens, slots)
+        self.be.dispatch(ent_g, [gu, x, gate[1], gate[0], moe_gate_pod_args(d, ffn, slots), gate[2], ids], grid, stream=st)
+        self.be.dispatch(ent_g, [gu.view(-1)[ffn:], x, up[1], up[0], moe_gate_pod_args(d, ffn, slots), up[2], ids], grid, stream=st)
+        self.be.silu_mul(h, gu, tokens * slots, ffn, stream=st)
+        self.be.dispatch(ent_d, [y_slots, h, down[1], down[0], moe_down_pod_args(d, ffn, slots), down[2], ids],
+                         (d // 4, tokens, slots), stream=st)
+
     def dense_ffn(self, x, gate, up, down, e, d, ffn, rows):
         """down_e(silu(gate_e x) * up_e x) for every row of x with ONE expert e of the stacks: plain projections."""
         dev = x.device
@@ -122,9 +134,11 @@ class NShardedProjection:
       fused=False  each rank computes its [M, per] block, one NCCL all-gather assembles the rows (any M);
       fused=True   decode form (M <= max_m <= 8): every rank holds the full output in symmetric memory and the GEMV of
                    rank r stores its shard into ALL ranks' outputs from inside the kernel (peer stores over NVLink),
-                   followed by one symmetric-memory barrier. No collective kernel, no staging copy. The outputs are
-                   double-buffered: the tensor returned by forward() is overwritten by the second forward() after it,
-                   so consume it (in stream order) before that.
+                   followed by one symmetric-memory barrier. No collective kernel, no staging copy. The outputs rotate
+                   over THREE buffers: a rank that has passed the barrier of forward n+1 may already be storing forward
+                   n+2 into its peers, and that lands in buffer (n+2) % 3, never in the one a slower peer is still
+                   reading from forward n. The tensor returned by forward() therefore stays valid until this rank's
+                   second forward() after it (it is overwritten by the third): consume it, in stream order, before then.
     """
 
     def __init__(self, kernels, W, scales, biases, N_total: int, K: int, *, out_f32: bool = False, group=None,
@@ -143,20 +157,20 @@ class NShardedProjection:
             assert 1 <= max_m <= 8
             dt = torch.float32 if out_f32 else torch.float16
             self.max_m, self._flip = max_m, 0
-            self._out = symm.empty((2, max_m, N_total), dtype=dt, device=W.device)
+            self._out = symm.empty((3, max_m, N_total), dtype=dt, device=W.device)
             g = group if group is not None else dist.group.WORLD
             self._hdl = symm.rendezvous(self._out, g.group_name)
             esz = 4 if out_f32 else 2
             # address of (buffer b, row 0, column lo) inside every rank's copy
             self._dst = [[int(base) + (bi * max_m * N_total + self.lo) * esz for base in self._hdl.buffer_ptrs]
-                         for bi in range(2)]
+                         for bi in range(3)]
 
     def forward(self, x: torch.Tensor, M: int) -> torch.Tensor:
         """x f16 [M, K] (replicated) -> y [M, N_total], every rank holding the whole output."""
         if self.fused:
             assert M <= self.max_m
             bi = self._flip
-            self._flip ^= 1
+            self._flip = (bi + 1) % 3
             if self.hi > self.lo:
                 self.k.matmul_multi(self._dst[bi], self.N_total, x, self.W, self.s, self.b, self.hi - self.lo, self.K, M,
                                     self.out_f32)
@@ -214,7 +228,7 @@ def plan_dispatch(ids_routed: torch.Tensor, experts_per_rank: int, world: int, g
 class ExpertParallelMoE:
     """Expert-parallel form of the block the engine runs as seven dispatches (engine-core.ts:2342-2349)."""
 
-    def __init__(self, kernels, gate, up, down, *, E: int, top_k: int, d: int, ffn: int, group=None):
+    def __init__(self, kernels, gate, up, down, *, E: int, top_k: int, d: int, ffn: int, group=None, max_tokens=None):
         """gate / up / down: (W, scales, biases) stacks of THIS rank: E/G routed experts followed by the shared one."""
         self.k, self.group = kernels, group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -223,6 +237,29 @@ class ExpertParallelMoE:
         self.E, self.top_k, self.d, self.ffn = E, top_k, d, ffn
         self.epr = E // self.world
         self.gate, self.up, self.down = gate, up, down
+        self.max_tokens = max_tokens
+        # One rank: there is nothing to dispatch, the block is the engine's own sequence of dispatches over the id list.
+        self.form = "one rank: router, gate, up, SiLU, down, combine over the id list" if self.world == 1 else \
+            "NCCL all-to-all of counts, rows and results (host reads the split sizes)"
+        self.capturable = self.world == 1      # no host round trip inside a step
+        self._bufs = {}
+
+    def _local_block(self, x: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
+        """world == 1: the shared expert is just slot K of every token (its id is E), as the engine runs it."""
+        T, K, d, ffn = x.shape[0], self.top_k, self.d, self.ffn
+        if T not in self._bufs:         # buffers are kept per token count, so a step can be replayed from a CUDA graph
+            dev = x.device
+            self._bufs[T] = dict(ids=torch.empty((T, K + 1), dtype=torch.int32, device=dev),
+                                 scores=torch.empty((T, K + 1), dtype=torch.float32, device=dev),
+                                 gu=torch.empty((T, K + 1, 2 * ffn), dtype=torch.float16, device=dev),
+                                 h=torch.empty((T, K + 1, ffn), dtype=torch.float16, device=dev),
+                                 y=torch.empty((T, K + 1, d), dtype=torch.float16, device=dev),
+                                 out=torch.empty((T, d), dtype=torch.float16, device=dev))
+        b = self._bufs[T]
+        self.k.route_topk(b["ids"], b["scores"], logits, self.E, K, T)
+        self.k.block_ffn(b["y"], b["gu"], b["h"], x, b["ids"], self.gate, self.up, self.down, d, ffn, T, K + 1)
+        self.k.combine(b["out"], b["y"], b["scores"], T, K + 1, d)
+        return b["out"]
 
     def _a2a(self, send: torch.Tensor, send_counts, recv_counts) -> torch.Tensor:
         out = torch.empty((sum(recv_counts),) + tuple(send.shape[1:]), dtype=send.dtype, device=send.device)
@@ -233,7 +270,9 @@ class ExpertParallelMoE:
         return out
 
     def forward(self, x: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
-        """x f16 [T_local, d], logits f32 [T_local, E+1] -> y f16 [T_local, d]."""
+        """x f16 [T_local, d], logits f32 [T_local, E+1] -> y f16 [T_local, d] (overwritten by the next forward)."""
+        if self.world == 1:
+            return self._local_block(x, logits)
         T, K, d = x.shape[0], self.top_k, self.d
         dev = x.device
         ids = torch.empty((T, K + 1), dtype=torch.int32, device=dev)

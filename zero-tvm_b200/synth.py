@@ -72,6 +72,14 @@ DENSE_LAYER_SET = [
 ]
 
 
+# The same layer as the engine dispatches it for decode: q, k, v rows concatenated into one projection and gate, up into
+# another (src/zero-tvm/engine-core.ts:1012-1018, :2290, :2517), so five launches instead of eight.
+DENSE_LAYER_SET_FUSED = [
+    ("qkv_proj", 6144, 4096, False), ("o_proj", 4096, 4096, False), ("gate_up_proj", 24576, 4096, False),
+    ("down_proj", 4096, 12288, False), ("lm_head", 151936, 4096, True),
+]
+
+
 def moe_block(T: int, *, E: int = 256, hidden: int = 2048, ffn: int = 512, bits: int = 4, group: int = 64,
               seed: int = 0, has_shared: bool = True):
     """Expert stacks (shared expert at index E), activations and router logits for T tokens."""
