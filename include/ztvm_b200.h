@@ -139,10 +139,9 @@ ZTVM_API ztvm_status ztvm_int4_matmul_moe(ztvm_ctx* ctx, const ztvm_moe_desc* de
  * buffer that grows on demand; this entry point keeps it in a fixed array inside the library's device image
  * and makes no allocating call at all.
  *  - Limits: tokens*slots <= ZTVM_MOE_NOALLOC_MAX_PAIRS and experts <= ZTVM_MOE_NOALLOC_MAX_EXPERTS, else
- *    ZTVM_ERR_TOO_LARGE. Only the two grouped kernels run here (there is no fall-back to the per-pair kernel):
- *    bits 4, group 64, and either K % 256 == 0, K <= 4096, N % 16 == 0 (streaming kernel) or K % 64 == 0,
- *    N % 128 == 0, output strides multiples of 8 elements, y 16-byte aligned (tensor-core tiles); input strides
- *    multiples of 8 elements. Anything else is ZTVM_ERR_UNSUPPORTED / ZTVM_ERR_ALIGNMENT. From 128 pairs on
+ *    ZTVM_ERR_TOO_LARGE. Only the grouped kernels run here (there is no fall-back to the per-pair kernel):
+ *    bits 4, group 64, K % 64 == 0, N % 8 == 0, input strides multiples of 8 elements. Anything else is
+ *    ZTVM_ERR_UNSUPPORTED / ZTVM_ERR_ALIGNMENT. From 128 pairs on
  *    (and with the ZTVM_MOE_GROUPED knob unset) the kernel is chosen exactly as ztvm_int4_matmul_moe chooses it, so
  *    the results are those of that call on the same inputs, bit for bit; below 128 pairs that call runs the per-pair
  *    GEMV instead, and the two agree within the path's tolerance only.
@@ -174,6 +173,59 @@ ZTVM_API ztvm_status ztvm_moe_route_topk(ztvm_ctx* ctx, uint32_t E, uint32_t K, 
 ZTVM_API ztvm_status ztvm_moe_dispatch_plan(ztvm_ctx* ctx, const uint32_t* ids, uint32_t tokens, uint32_t slots,
                                    uint32_t ids_stride, uint32_t experts, uint32_t experts_per_rank, uint32_t world,
                                    int64_t* order, int32_t* local_expert, int64_t* send_counts, void* stream);
+
+/* ---- expert-parallel form (experts dealt to `world` ranks in contiguous runs; one process per GPU) -------------------
+ * The reference runs the whole block on one device and has no counterpart for these three entry points. They keep the
+ * host out of the step: rows travel by stores to peer-mapped memory from inside the kernels, every count stays on
+ * the device, and the step can be captured in a CUDA graph. Ordering between ranks is the caller's: a device-side
+ * barrier after ztvm_moe_ep_dispatch (all rows have landed) and one after the down projection (all results are back).
+ *
+ * Receive buffers of a rank: world + 1 regions of seg_cap rows each. Region s < world is written by rank s only;
+ * region `world` is local (one row per token for the replicated shared expert). recv_x f16[regions][seg_cap][d],
+ * recv_ids u32[regions][seg_cap] (index of the row's expert inside the receiver's stack), recv_src u32[regions][seg_cap]
+ * (token * (top_k + has_shared) + slot on the source rank: where the result row belongs there), recv_cnt
+ * u32[regions]. The arrays below hold EVERY rank's buffers as mapped in this process (entry `rank` = its own). */
+typedef struct ztvm_moe_ep_layout {
+  uint32_t world, rank, experts_per_rank, seg_cap;
+  void* recv_x[8];
+  uint32_t* recv_ids[8];
+  uint32_t* recv_src[8];
+  uint32_t* recv_cnt[8];
+  uint32_t* cursors;   /* this rank's own scratch: world + 2 words, zero before the first step (kept zero by the calls) */
+} ztvm_moe_ep_layout;
+
+/* Sends every routed pair (token, slot < top_k) of ids u32[tokens][ids_stride] to the owner of its expert: the token's
+ * activation row x[token] (d f16, rows x_tok_stride apart; d % 8 == 0) plus the two index words, and publishes the
+ * counts. With has_shared, each token's row also goes into the local region for the shared expert (stack index
+ * experts_per_rank). seg_cap >= tokens * top_k (and >= tokens). Ids outside [0, world * experts_per_rank) are counted
+ * (ztvm_device_errors) and dropped. */
+ZTVM_API ztvm_status ztvm_moe_ep_dispatch(ztvm_ctx* ctx, const ztvm_moe_ep_layout* layout, const uint32_t* ids,
+                                 uint32_t tokens, uint32_t top_k, uint32_t has_shared, uint32_t ids_stride, const void* x,
+                                 uint32_t d, uint32_t x_tok_stride, void* stream);
+
+/* How the rows of an expert-parallel id list are laid out, for ztvm_int4_matmul_moe_ep and ztvm_silu_mul_rows. */
+typedef struct ztvm_moe_ep_rows {
+  const uint32_t* seg_counts;  /* live rows of each region (recv_cnt) */
+  uint32_t seg_cap;            /* rows per region */
+  uint32_t segments;           /* regions: desc->tokens == segments * seg_cap */
+  const uint32_t* dst_index;   /* NULL: results go to y as in ztvm_int4_matmul_moe. Else (recv_src) the result row of entry
+                                  i goes to y_seg[i / seg_cap] + dst_index[i] * out_tok_stride elements */
+  void* y_seg[9];              /* with dst_index: output base of every region's source rank, as mapped in this process */
+  uint32_t reuse_plan;         /* 1: ids, tokens and seg_counts are those of the previous call on this context (gate, up
+                                  and down of one step share one id list): its expert-sorted plan is used again */
+} ztvm_moe_ep_rows;
+
+/* ztvm_int4_matmul_moe over a receive buffer: one id per row (desc->slots must be 1), only the live prefix of each
+ * region is computed; entries past it are skipped without being counted as bad ids. Runs the grouped kernels only
+ * (bits 4, group 64, K % 64 == 0); with dst_index the tensor-core tiles, whose epilogue stores each result row
+ * straight to the rank it came from. */
+ZTVM_API ztvm_status ztvm_int4_matmul_moe_ep(ztvm_ctx* ctx, const ztvm_moe_desc* desc, const ztvm_moe_ep_rows* rows, void* y,
+                                    const void* x, const void* scales, const void* packed_w, const void* biases,
+                                    const uint32_t* ids, void* stream);
+
+/* ztvm_silu_mul over the live rows of a receive buffer (rows == segments * seg_cap). */
+ZTVM_API ztvm_status ztvm_silu_mul_rows(ztvm_ctx* ctx, const ztvm_moe_ep_rows* rows, uint32_t ffn, void* h, const void* gate_up,
+                               void* stream);
 
 /* h[r][i] = f16(up * gate * 1/(1+exp(-gate))) over rows of [gate(ffn) | up(ffn)] f16.
  * Replaces silu_mul (src/compiler/shaders/silu_mul.wgsl:26-44). */

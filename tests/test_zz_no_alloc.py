@@ -28,8 +28,8 @@ def check_against_oracle(oracle_c, y_bits, mb, ids, tiles):
     assert err <= TOL, f"rel err {err:.3e}"
 
 
-def moe_desc(K, N, experts, slots, tokens, in_slot, out_slot, in_tok, out_tok):
-    return z.MoeDesc(z.MmDesc(K, N, 1, 64, 4, 1, 0), experts, slots, tokens, in_slot, out_slot, in_tok, out_tok, slots)
+def moe_desc(K, N, experts, slots, tokens, in_slot, out_slot, in_tok, out_tok, bits=4):
+    return z.MoeDesc(z.MmDesc(K, N, 1, 64, bits, 1, 0), experts, slots, tokens, in_slot, out_slot, in_tok, out_tok, slots)
 
 
 def both_entries(backend, dev, mb, ids, slots, seed_fill):
@@ -112,7 +112,7 @@ def test_noalloc_refuses_what_does_not_fit_or_is_not_a_tile_shape(backend, dev):
     # refusals happen before any launch, so the (too small) buffers above are never touched
     for kw, code, word in ((dict(tokens=65536 // 3 + 1), z.capi.ERR_TOO_LARGE, "65536"),
                            (dict(experts=1025), z.capi.ERR_TOO_LARGE, "1024"),
-                           (dict(N=72), z.capi.ERR_UNSUPPORTED, "N"),
+                           (dict(bits=3), z.capi.ERR_UNSUPPORTED, "bits"),
                            (dict(in_tok=252), z.capi.ERR_ALIGNMENT, "strides")):
         with pytest.raises(z.ZtvmError) as e:
             call(**kw)

@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "libztvm_b200.so")
-SOURCES = ["ztvm_api.cu", "ztvm_gemv.cu", "ztvm_gemv_mma.cu", "ztvm_gemv_tc.cu", "ztvm_gemv_tc3.cu", "ztvm_gemm.cu", "ztvm_gemm_ta.cu", "ztvm_moe_gemm.cu", "ztvm_moe_tc.cu", "ztvm_glue.cu"]
+SOURCES = ["ztvm_api.cu", "ztvm_gemv.cu", "ztvm_gemv_mma.cu", "ztvm_gemv_tc.cu", "ztvm_gemv_tc3.cu", "ztvm_gemm.cu", "ztvm_gemm_ta.cu", "ztvm_moe_gemm.cu", "ztvm_moe_ta.cu", "ztvm_moe_ep.cu", "ztvm_moe_tc.cu", "ztvm_glue.cu"]
 HEADERS = ["ztvm_device.cuh", "ztvm_tc.cuh", "ztvm_stream_mma.cuh", "ztvm_moe_plan.cuh", "ztvm_kernels.h", os.path.join("..", "..", "include", "ztvm_b200.h")]
 
 NVCC_FLAGS = [

@@ -9,13 +9,15 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libztvm_b200.so")
+# ZTVM_LIB: path of another build of the same library (A/B measurements of build-time variants)
+LIB_PATH = os.environ.get("ZTVM_LIB") or os.path.join(_HERE, "lib", "libztvm_b200.so")
 
 # every symbol include/ztvm_b200.h declares
 SYMBOLS = [
     "ztvm_version", "ztvm_status_string", "ztvm_init", "ztvm_destroy", "ztvm_last_error", "ztvm_sync",
     "ztvm_int4_matmul", "ztvm_int4_matmul_multi", "ztvm_int4_matmul_host", "ztvm_int4_matmul_moe", "ztvm_int4_matmul_moe_noalloc",
-    "ztvm_moe_route_topk", "ztvm_moe_dispatch_plan", "ztvm_silu_mul",
+    "ztvm_moe_route_topk", "ztvm_moe_dispatch_plan", "ztvm_moe_ep_dispatch", "ztvm_int4_matmul_moe_ep", "ztvm_silu_mul_rows",
+    "ztvm_silu_mul",
     "ztvm_moe_combine", "ztvm_unpack_codes", "ztvm_unpack_codes_streamed", "ztvm_dequant", "ztvm_device_errors",
 ]
 
@@ -36,6 +38,19 @@ class MoeDesc(C.Structure):
     _fields_ = [("mm", MmDesc)] + [(n, C.c_uint32) for n in (
         "experts", "slots", "tokens", "in_slot_stride", "out_slot_stride", "in_tok_stride", "out_tok_stride",
         "ids_stride")]
+
+
+class MoeEpLayout(C.Structure):
+    """Receive buffers of every rank as mapped in this process (include/ztvm_b200.h: ztvm_moe_ep_layout)."""
+    _fields_ = [(n, C.c_uint32) for n in ("world", "rank", "experts_per_rank", "seg_cap")] + [
+        ("recv_x", C.c_void_p * 8), ("recv_ids", C.c_void_p * 8), ("recv_src", C.c_void_p * 8), ("recv_cnt", C.c_void_p * 8),
+        ("cursors", C.c_void_p)]
+
+
+class MoeEpRows(C.Structure):
+    """Layout of an expert-parallel id list (include/ztvm_b200.h: ztvm_moe_ep_rows)."""
+    _fields_ = [("seg_counts", C.c_void_p), ("seg_cap", C.c_uint32), ("segments", C.c_uint32), ("dst_index", C.c_void_p),
+                ("y_seg", C.c_void_p * 9), ("reuse_plan", C.c_uint32)]
 
 
 _lib = None
@@ -67,6 +82,9 @@ def load() -> C.CDLL:
         "ztvm_int4_matmul_moe_noalloc": [vp, C.POINTER(MoeDesc), vp, vp, vp, vp, vp, vp, vp],
         "ztvm_moe_route_topk": [vp, u32, u32, u32, u32, u32, vp, vp, vp, vp],
         "ztvm_moe_dispatch_plan": [vp, vp, u32, u32, u32, u32, u32, u32, vp, vp, vp, vp],
+        "ztvm_moe_ep_dispatch": [vp, C.POINTER(MoeEpLayout), vp, u32, u32, u32, u32, vp, u32, u32, vp],
+        "ztvm_int4_matmul_moe_ep": [vp, C.POINTER(MoeDesc), C.POINTER(MoeEpRows), vp, vp, vp, vp, vp, vp, vp],
+        "ztvm_silu_mul_rows": [vp, C.POINTER(MoeEpRows), u32, vp, vp, vp],
         "ztvm_silu_mul": [vp, u32, u32, vp, vp, vp],
         "ztvm_moe_combine": [vp, u32, u32, u32, vp, vp, vp, vp],
         "ztvm_unpack_codes": [vp, C.POINTER(MmDesc), vp, vp, vp],
@@ -165,6 +183,17 @@ class Context:
                           send_counts, stream=None):
         check(self._lib.ztvm_moe_dispatch_plan(self.handle, ptr(ids), tokens, slots, ids_stride, experts, experts_per_rank,
                                                world, ptr(order), ptr(local_expert), ptr(send_counts), stream_ptr(stream)))
+
+    def moe_ep_dispatch(self, layout: MoeEpLayout, ids, tokens, top_k, has_shared, ids_stride, x, d, x_tok_stride, stream=None):
+        check(self._lib.ztvm_moe_ep_dispatch(self.handle, C.byref(layout), ptr(ids), tokens, top_k, int(has_shared), ids_stride,
+                                             ptr(x), d, x_tok_stride, stream_ptr(stream)))
+
+    def int4_matmul_moe_ep(self, desc: MoeDesc, rows: MoeEpRows, y, x, scales, packed_w, biases, ids, stream=None):
+        check(self._lib.ztvm_int4_matmul_moe_ep(self.handle, C.byref(desc), C.byref(rows), ptr(y), ptr(x), ptr(scales),
+                                                ptr(packed_w), ptr(biases), ptr(ids), stream_ptr(stream)))
+
+    def silu_mul_rows(self, rows: MoeEpRows, ffn, h, gate_up, stream=None):
+        check(self._lib.ztvm_silu_mul_rows(self.handle, C.byref(rows), ffn, ptr(h), ptr(gate_up), stream_ptr(stream)))
 
     def silu_mul(self, rows, ffn, h, gate_up, stream=None):
         check(self._lib.ztvm_silu_mul(self.handle, rows, ffn, ptr(h), ptr(gate_up), stream_ptr(stream)))

@@ -31,6 +31,9 @@ struct ztvm_ctx {
   // grouped kernel; unset = by size (below 128 pairs per-pair; then streaming while an expert sees few pairs)
   int moe_grouped;
   int gemm_sm;      // env ZTVM_GEMM=sm: the GEMM with both operands in shared memory (a measurement knob)
+  // what the plan in d_ws was built from (ztvm_int4_matmul_moe_ep reuse_plan)
+  const void* plan_ids; const void* plan_segs; uint32_t plan_tokens, plan_tile_rows, plan_experts;
+  int moe_tiles_sm; // env ZTVM_MOE_TILES=sm: the grouped MoE tiles with both operands in shared memory (a measurement knob)
 };
 
 namespace {
@@ -197,6 +200,8 @@ ztvm_status ztvm_init(int32_t device_ordinal, ztvm_ctx** out_ctx) {
   c->no_gemm = (ng && ng[0] == '1') ? 1 : 0;
   const char* gk = getenv("ZTVM_GEMM");
   c->gemm_sm = (gk && !strcmp(gk, "sm")) ? 1 : 0;
+  const char* mt = getenv("ZTVM_MOE_TILES");
+  c->moe_tiles_sm = (mt && !strcmp(mt, "sm")) ? 1 : 0;
   const char* mg = getenv("ZTVM_MOE_GROUPED");
   c->moe_grouped = !mg ? -1 : (mg[0] == '1' ? 1 : mg[0] == '2' ? 2 : 0);
   const char* gp = getenv("ZTVM_GEMV_PATH");
@@ -314,18 +319,22 @@ ztvm_status ztvm_int4_matmul_host(ztvm_ctx* ctx, const ztvm_mm_desc* d, void* y_
   return ZTVM_OK;
 }
 
-// Which grouped kernel serves a MoE launch: 0 none (per-pair GEMV), 1 tensor-core tiles, 2 streaming kernel.
-// `forced` is the context's ZTVM_MOE_GROUPED knob (-1 = by size).
-static int moe_pick(int forced, const ztvm_moe_desc* md, const ztvm::GemvParams& p, const void* y) {
+// Which grouped kernel serves a MoE launch: 0 none (per-pair GEMV), 1 tensor-core tiles with the weights in tensor
+// memory, 2 streaming kernel, 3 tensor-core tiles with both operands in shared memory (ZTVM_MOE_TILES=sm, or shapes
+// only it takes). `forced` is the context's ZTVM_MOE_GROUPED knob (-1 = by size).
+static int moe_pick(const ztvm_ctx* ctx, const ztvm_moe_desc* md, const ztvm::GemvParams& p, const void* y) {
+  const int forced = ctx->moe_grouped;
   const ztvm_mm_desc* d = &md->mm;
   const uint64_t pairs = (uint64_t)md->tokens * md->slots;
-  const bool tiles_ok = (md->out_slot_stride | md->out_tok_stride) % 8 == 0 && aligned(y, 16) &&
-                        ztvm::moe_grouped_supported((int)d->bits, d->group, d->K, d->N, md->experts);
-  const bool stream_ok = ztvm::moe_tc_supported(p, (int)d->bits);
+  const bool ta_ok = ztvm::moe_ta_supported((int)d->bits, d->group, d->K, d->N, md->experts);
+  const bool sm_ok = (md->out_slot_stride | md->out_tok_stride) % 8 == 0 && aligned(y, 16) && !p.dst_index &&
+                     ztvm::moe_grouped_supported((int)d->bits, d->group, d->K, d->N, md->experts);
+  const int tiles = ctx->moe_tiles_sm ? (sm_ok ? 3 : ta_ok ? 1 : 0) : (ta_ok ? 1 : sm_ok ? 3 : 0);
+  const bool stream_ok = ztvm::moe_tc_supported(p, (int)d->bits) && !p.dst_index;
   const bool few_per_expert = pairs < 24ull * md->experts;
-  if (forced == 1) return tiles_ok ? 1 : stream_ok ? 2 : 0;
-  if (forced == 2) return stream_ok ? 2 : tiles_ok ? 1 : 0;
-  return (stream_ok && (few_per_expert || !tiles_ok)) ? 2 : tiles_ok ? 1 : 0;
+  if (forced == 1) return tiles ? tiles : stream_ok ? 2 : 0;
+  if (forced == 2) return stream_ok ? 2 : tiles;
+  return (stream_ok && (few_per_expert || !tiles)) ? 2 : tiles;
 }
 
 static ztvm::GemvParams moe_params(ztvm_ctx* ctx, const ztvm_moe_desc* md, void* y, const void* x, const void* scales,
@@ -370,15 +379,18 @@ ztvm_status ztvm_int4_matmul_moe(ztvm_ctx* ctx, const ztvm_moe_desc* md, void* y
   const bool want_grouped = ctx->moe_grouped < 0 ? pairs >= 128 : ctx->moe_grouped >= 1;
   if (want_grouped && pairs < (1ull << 31)) {
     const ztvm::GemvParams p = moe_params(ctx, md, y, x, scales, packed_w, biases, ids);
-    const int pick = moe_pick(ctx->moe_grouped, md, p, y);
+    const int pick = moe_pick(ctx, md, p, y);
     if (pick) {
       const size_t need = ztvm::moe_grouped_scratch_bytes(md->experts, (uint32_t)pairs);
       if (ctx->d_ws_bytes < need) {
         ZTVM_CUDA(cudaDeviceSynchronize());
         if ((s = grow(&ctx->d_ws, &ctx->d_ws_bytes, need, false))) return s;
       }
-      if (pick == 2) ZTVM_CUDA(ztvm::launch_moe_tc(p, md->tokens, md->slots, static_cast<uint32_t*>(ctx->d_ws), ctx->sm_count, st));
-      else ZTVM_CUDA(ztvm::launch_moe_grouped(p, md->tokens, md->slots, static_cast<uint32_t*>(ctx->d_ws), ctx->err_counter + 1, st));
+      ctx->plan_ids = nullptr;      // the plan buffer is rebuilt below: nothing to reuse from an earlier call
+      uint32_t* ws = static_cast<uint32_t*>(ctx->d_ws);
+      if (pick == 2) ZTVM_CUDA(ztvm::launch_moe_tc(p, md->tokens, md->slots, ws, ctx->sm_count, st));
+      else if (pick == 1) ZTVM_CUDA(ztvm::launch_moe_ta(p, md->tokens, md->slots, ws, ctx->err_counter + 1, ctx->sm_count, st));
+      else ZTVM_CUDA(ztvm::launch_moe_grouped(p, md->tokens, md->slots, ws, ctx->err_counter + 1, st));
       return ZTVM_OK;
     }
   }
@@ -427,13 +439,13 @@ ztvm_status ztvm_int4_matmul_moe_noalloc(ztvm_ctx* ctx, const ztvm_moe_desc* md,
     return fail(ZTVM_ERR_ALIGNMENT, "input strides must be multiples of 8 elements (16-byte activation loads)");
   cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : ctx->stream;
   const ztvm::GemvParams p = moe_params(ctx, md, y, x, scales, packed_w, biases, ids);
-  const int pick = moe_pick(ctx->moe_grouped, md, p, y);   // the same choice ztvm_int4_matmul_moe makes
+  const int pick = moe_pick(ctx, md, p, y);   // the same choice ztvm_int4_matmul_moe makes
   if (!pick)
     return fail(ZTVM_ERR_UNSUPPORTED,
-                "this entry point runs the grouped kernels only: bits=4, group=64, and either K %% 256 == 0, K <= 4096, "
-                "N %% 16 == 0 or K %% 64 == 0, N %% 128 == 0 with y 16-byte aligned and output strides multiples of 8 "
+                "this entry point runs the grouped kernels only: bits=4, group=64, K %% 64 == 0, N %% 8 == 0 "
                 "(got bits=%u group=%u K=%u N=%u)", d->bits, d->group, d->K, d->N);
   if (pick == 2) ZTVM_CUDA(ztvm::launch_moe_tc_static(p, md->tokens, md->slots, ctx->sm_count, st));
+  else if (pick == 1) ZTVM_CUDA(ztvm::launch_moe_ta_static(p, md->tokens, md->slots, ctx->err_counter + 1, ctx->sm_count, st));
   else ZTVM_CUDA(ztvm::launch_moe_grouped_static(p, md->tokens, md->slots, ctx->err_counter + 1, st));
   return ZTVM_OK;
 }
@@ -473,6 +485,7 @@ ztvm_status ztvm_moe_dispatch_plan(ztvm_ctx* ctx, const uint32_t* ids, uint32_t 
     ZTVM_CUDA(cudaDeviceSynchronize());
     if ((s = grow(&ctx->d_ws, &ctx->d_ws_bytes, need, false))) return s;
   }
+  ctx->plan_ids = nullptr;
   ztvm::GemvParams p;
   memset(&p, 0, sizeof(p));
   p.ids = ids;
@@ -482,6 +495,101 @@ ztvm_status ztvm_moe_dispatch_plan(ztvm_ctx* ctx, const uint32_t* ids, uint32_t 
   ZTVM_CUDA(ztvm::launch_moe_dispatch_plan(p, tokens, slots, experts_per_rank, world, static_cast<uint32_t*>(ctx->d_ws),
                                            reinterpret_cast<long long*>(order), local_expert,
                                            reinterpret_cast<long long*>(send_counts), st));
+  return ZTVM_OK;
+}
+
+ztvm_status ztvm_moe_ep_dispatch(ztvm_ctx* ctx, const ztvm_moe_ep_layout* L, const uint32_t* ids, uint32_t tokens,
+                                 uint32_t top_k, uint32_t has_shared, uint32_t ids_stride, const void* x, uint32_t d,
+                                 uint32_t x_tok_stride, void* stream) {
+  ztvm_status s = check_ctx(ctx);
+  if (s) return s;
+  if (!L || !ids || !x) return fail(ZTVM_ERR_NULL_POINTER, "layout/ids/x must be non-NULL");
+  if (L->world == 0 || L->world > 8 || L->rank >= L->world) return fail(ZTVM_ERR_BAD_DIMS, "world=%u rank=%u: 1..8 ranks", L->world, L->rank);
+  if (L->experts_per_rank == 0 || top_k == 0 || ids_stride < top_k + (has_shared ? 1u : 0u))
+    return fail(ZTVM_ERR_BAD_DIMS, "experts_per_rank=%u top_k=%u ids_stride=%u", L->experts_per_rank, top_k, ids_stride);
+  if (d == 0 || d % 8 || x_tok_stride % 8 || !aligned(x, 16)) return fail(ZTVM_ERR_ALIGNMENT, "rows are copied in 16-byte pieces: d, x_tok_stride multiples of 8, x 16-byte aligned");
+  if ((uint64_t)tokens * top_k > L->seg_cap || tokens > L->seg_cap)
+    return fail(ZTVM_ERR_TOO_LARGE, "tokens*top_k=%llu exceeds seg_cap=%u", (unsigned long long)tokens * top_k, L->seg_cap);
+  if (!L->cursors) return fail(ZTVM_ERR_NULL_POINTER, "layout.cursors is NULL");
+  for (uint32_t r = 0; r < L->world; ++r)
+    if (!L->recv_x[r] || !L->recv_ids[r] || !L->recv_src[r] || !L->recv_cnt[r] || !aligned(L->recv_x[r], 16))
+      return fail(ZTVM_ERR_NULL_POINTER, "receive buffers of rank %u missing or misaligned", r);
+  if (tokens == 0) return ZTVM_OK;
+  cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : ctx->stream;
+  ztvm::EpDispatchParams p;
+  memset(&p, 0, sizeof(p));
+  p.ids = ids; p.x = static_cast<const __half*>(x);
+  p.tokens = tokens; p.top_k = top_k; p.has_shared = has_shared ? 1u : 0u; p.ids_stride = ids_stride;
+  p.slots_total = top_k + p.has_shared; p.d = d; p.x_tok_stride = x_tok_stride;
+  p.epr = L->experts_per_rank; p.world = L->world; p.rank = L->rank; p.seg_cap = L->seg_cap;
+  for (uint32_t r = 0; r < L->world; ++r) {
+    p.recv_x[r] = static_cast<__half*>(L->recv_x[r]); p.recv_ids[r] = L->recv_ids[r];
+    p.recv_src[r] = L->recv_src[r]; p.recv_cnt[r] = L->recv_cnt[r];
+  }
+  p.cursors = L->cursors; p.err = ctx->err_counter;
+  ZTVM_CUDA(ztvm::launch_moe_ep_dispatch(p, ctx->sm_count, st));
+  return ZTVM_OK;
+}
+
+ztvm_status ztvm_int4_matmul_moe_ep(ztvm_ctx* ctx, const ztvm_moe_desc* md, const ztvm_moe_ep_rows* rows, void* y,
+                                    const void* x, const void* scales, const void* packed_w, const void* biases,
+                                    const uint32_t* ids, void* stream) {
+  ztvm_status s = check_ctx(ctx);
+  if (s) return s;
+  if (!md || !rows) return fail(ZTVM_ERR_NULL_POINTER, "desc/rows is NULL");
+  const ztvm_mm_desc* d = &md->mm;
+  if ((s = check_desc(d, false))) return s;
+  if (!d->affine || d->out_f32 || d->M > 1) return fail(ZTVM_ERR_UNSUPPORTED, "MoE expert matmuls are affine, f16 out, one row per pair");
+  if (md->slots != 1) return fail(ZTVM_ERR_BAD_DIMS, "a receive buffer holds one id per row: slots must be 1 (got %u)", md->slots);
+  if (!rows->seg_counts || rows->seg_cap == 0 || rows->segments == 0 || rows->segments > 9 ||
+      (uint64_t)rows->segments * rows->seg_cap != md->tokens)
+    return fail(ZTVM_ERR_BAD_DIMS, "segments=%u x seg_cap=%u must equal tokens=%u (at most 9 regions)", rows->segments, rows->seg_cap, md->tokens);
+  void* y_check = y;
+  if (rows->dst_index) {
+    for (uint32_t i = 0; i < rows->segments; ++i)
+      if (!rows->y_seg[i]) return fail(ZTVM_ERR_NULL_POINTER, "y_seg[%u] is NULL", i);
+    y_check = rows->y_seg[0];
+  }
+  if ((s = check_buffers(d, y_check, x, scales, packed_w, biases))) return s;
+  if (!ids) return fail(ZTVM_ERR_NULL_POINTER, "ids is NULL");
+  if (md->experts == 0 || md->ids_stride < 1) return fail(ZTVM_ERR_BAD_DIMS, "experts and ids_stride must be non-zero");
+  if ((md->in_slot_stride | md->in_tok_stride) % 8)
+    return fail(ZTVM_ERR_ALIGNMENT, "input strides must be multiples of 8 elements (16-byte activation loads)");
+  if ((uint64_t)md->tokens >= (1ull << 31)) return fail(ZTVM_ERR_TOO_LARGE, "tokens=%u", md->tokens);
+  cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : ctx->stream;
+  ztvm::GemvParams p = moe_params(ctx, md, y_check, x, scales, packed_w, biases, ids);
+  p.seg_counts = rows->seg_counts; p.seg_cap = rows->seg_cap; p.dst_index = rows->dst_index;
+  for (uint32_t i = 0; i < rows->segments; ++i) p.y_seg[i] = rows->y_seg[i];
+  const int pick = moe_pick(ctx, md, p, y_check);
+  if (pick != 1 && pick != 2)
+    return fail(ZTVM_ERR_UNSUPPORTED, "the expert-parallel form runs the grouped kernels only: bits=4, group=64, K %% 64 == 0 "
+                "(got bits=%u group=%u K=%u N=%u)", d->bits, d->group, d->K, d->N);
+  const size_t need = ztvm::moe_grouped_scratch_bytes(md->experts, md->tokens);
+  if (ctx->d_ws_bytes < need) {
+    ZTVM_CUDA(cudaDeviceSynchronize());
+    if ((s = grow(&ctx->d_ws, &ctx->d_ws_bytes, need, false))) return s;
+    ctx->plan_ids = nullptr;
+  }
+  const uint32_t tile_rows = pick == 1 ? ztvm::kMoeTaTileRows : ztvm::kMoeTcTileRows;
+  const bool reuse = rows->reuse_plan && ctx->plan_ids == ids && ctx->plan_segs == rows->seg_counts &&
+                     ctx->plan_tokens == md->tokens && ctx->plan_tile_rows == tile_rows && ctx->plan_experts == md->experts;
+  uint32_t* ws = static_cast<uint32_t*>(ctx->d_ws);
+  if (pick == 2) ZTVM_CUDA(ztvm::launch_moe_tc(p, md->tokens, 1, ws, ctx->sm_count, st, reuse));
+  else ZTVM_CUDA(ztvm::launch_moe_ta(p, md->tokens, 1, ws, ctx->err_counter + 1, ctx->sm_count, st, reuse));
+  ctx->plan_ids = ids; ctx->plan_segs = rows->seg_counts; ctx->plan_tokens = md->tokens;
+  ctx->plan_tile_rows = tile_rows; ctx->plan_experts = md->experts;
+  return ZTVM_OK;
+}
+
+ztvm_status ztvm_silu_mul_rows(ztvm_ctx* ctx, const ztvm_moe_ep_rows* rows, uint32_t ffn, void* h, const void* gate_up,
+                               void* stream) {
+  ztvm_status s = check_ctx(ctx);
+  if (s) return s;
+  if (!rows || !h || !gate_up) return fail(ZTVM_ERR_NULL_POINTER, "rows/h/gate_up must be non-NULL");
+  if (ffn == 0 || !rows->seg_counts || rows->seg_cap == 0) return fail(ZTVM_ERR_BAD_DIMS, "ffn, seg_counts and seg_cap must be set");
+  cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : ctx->stream;
+  ZTVM_CUDA(ztvm::launch_silu_mul(static_cast<const __half*>(gate_up), static_cast<__half*>(h), rows->segments * rows->seg_cap,
+                                  ffn, st, rows->seg_counts, rows->seg_cap));
   return ZTVM_OK;
 }
 

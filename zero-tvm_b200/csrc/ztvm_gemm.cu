@@ -285,17 +285,14 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
             s16 = __ldg(srow + g);
             if (AFFINE) b16 = __ldg(brow + g);
           }
-          float sf = __half2float(__ushort_as_half(s16));
-          float bf = __half2float(__ushort_as_half(b16));
+          DqGroup dq = dq_group<AFFINE>(s16, b16);
 #pragma unroll
           for (int wi = 0; wi < WPT; ++wi) {
             if (WPT == 8 && wi == 4 && gshift == 5) {   // group 32: the second half of the block is the next group
               const uint32_t g = (kb * kGemmBK + 32) >> gshift;
-              s16 = __ldg(srow + g);
-              sf = __half2float(__ushort_as_half(s16));
-              bf = AFFINE ? __half2float(__ushort_as_half(__ldg(brow + g))) : 0.f;
+              dq = dq_group<AFFINE>(__ldg(srow + g), AFFINE ? __ldg(brow + g) : (unsigned short)0);
             }
-            const uint4 v = dequant_word_w16<AFFINE>(wv[wi], s16, sf, bf);
+            const uint4 v = dequant_word_w16<AFFINE>(wv[wi], dq);
             const uint32_t chunk = part * WPT + wi;                      // 16-byte chunk of the 128-byte row
             *reinterpret_cast<uint4*>(rowp + ((chunk ^ (r_tile & 7)) << 4)) = v;
           }

@@ -44,21 +44,6 @@ struct GemmTaSmem {
   static constexpr int kTotal = kOffBar + 256;
 };
 
-__device__ __forceinline__ void umma_f16_ta(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(acc) : "memory");
-}
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
-      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
-        "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
-      : "memory");
-}
-__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-
 template <int NT, bool AFFINE>
 __global__ void __launch_bounds__(kTaThreads, 1)
 gemm_w4_ta_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
@@ -248,12 +233,12 @@ gemm_w4_ta_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
             s16 = __ldg(srow + g);
             if (AFFINE) b16 = __ldg(brow + g);
           }
-          const float sf = __half2float(__ushort_as_half(s16)), bf = __half2float(__ushort_as_half(b16));
+          const DqGroup dq = dq_group<AFFINE>(s16, b16);
           const uint32_t words[4] = {wv.x, wv.y, wv.z, wv.w};
           uint32_t a[16];
 #pragma unroll
           for (int wi = 0; wi < 4; ++wi) {
-            const uint4 v = dequant_word_w16<AFFINE>(words[wi], s16, sf, bf);
+            const uint4 v = dequant_word_w16<AFFINE>(words[wi], dq);
             a[4 * wi] = v.x; a[4 * wi + 1] = v.y; a[4 * wi + 2] = v.z; a[4 * wi + 3] = v.w;
           }
           // 32 weights of this row = 16 TMEM columns (two k-adjacent f16 per column) of this thread's lane

@@ -55,8 +55,7 @@ __global__ void dequant_kernel(const uint32_t* W, const __half* S, const __half*
       // the tensor-core GEMMs (dense and grouped) build their f16 operand with dequant_word_w16: so does the hook
       const unsigned short s16 = reinterpret_cast<const unsigned short*>(S)[(size_t)n * SPR + g];
       const unsigned short b16 = AFFINE ? reinterpret_cast<const unsigned short*>(B)[(size_t)n * SPR + g] : (unsigned short)0;
-      const uint4 v = dequant_word_w16<AFFINE>(W[(size_t)n * KP + blk], s16, __half2float(__ushort_as_half(s16)),
-                                               __half2float(__ushort_as_half(b16)));
+      const uint4 v = dequant_word_w16<AFFINE>(W[(size_t)n * KP + blk], dq_group<AFFINE>(s16, b16));
       *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(out) + i * 8) = v;
       continue;
     }
@@ -240,20 +239,23 @@ cudaError_t launch_route_topk(const float* logits, uint32_t* ids, float* scores,
 
 // ---- SiLU * up -----------------------------------------------------------------------------------
 // Rows of [gate(ffn) | up(ffn)] f16 -> f16 [ffn]; f32 arithmetic (silu_mul.wgsl:40-43).
-__global__ void silu_mul_kernel(const __half* __restrict__ gate_up, __half* __restrict__ h, uint32_t rows, uint32_t ffn) {
+__global__ void silu_mul_kernel(const __half* __restrict__ gate_up, __half* __restrict__ h, uint32_t rows, uint32_t ffn,
+                                const uint32_t* __restrict__ seg_counts, uint32_t seg_cap) {
   const size_t total = (size_t)rows * ffn;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const size_t r = i / ffn, c = i - r * ffn;
+    if (seg_counts && (uint32_t)(r % seg_cap) >= seg_counts[r / seg_cap]) continue;   // past the region's live rows
     const float g = __half2float(gate_up[r * 2 * ffn + c]);
     const float u = __half2float(gate_up[r * 2 * ffn + ffn + c]);
     const float sg = g * (1.0f / (1.0f + expf(-g)));
     h[i] = __float2half_rn(u * sg);
   }
 }
-cudaError_t launch_silu_mul(const __half* gate_up, __half* h, uint32_t rows, uint32_t ffn, cudaStream_t st) {
+cudaError_t launch_silu_mul(const __half* gate_up, __half* h, uint32_t rows, uint32_t ffn, cudaStream_t st,
+                            const uint32_t* seg_counts, uint32_t seg_cap) {
   const size_t total = (size_t)rows * ffn;
   if (total == 0) return cudaSuccess;
-  silu_mul_kernel<<<grid_for(total, 256), 256, 0, st>>>(gate_up, h, rows, ffn);
+  silu_mul_kernel<<<grid_for(total, 256), 256, 0, st>>>(gate_up, h, rows, ffn, seg_counts, seg_cap ? seg_cap : 1u);
   return cudaGetLastError();
 }
 

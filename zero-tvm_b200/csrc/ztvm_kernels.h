@@ -26,6 +26,14 @@ struct GemvParams {
   // further destinations of the output (same layout as Y): peers' copies of a sharded projection's result
   void* y_more[7];
   uint32_t n_more;
+  // Expert-parallel form of the grouped MoE matmuls (one entry of `ids` per row, slots = 1): the id list is made of
+  // regions of seg_cap entries, one per source rank, of which only the first seg_counts[region] are live (the others
+  // are skipped without being counted as bad ids); with dst_index set, the output row of entry i goes to
+  // y_seg[i / seg_cap] + dst_index[i] * out_tok_stride (the buffers of the ranks the rows came from).
+  const uint32_t* seg_counts;
+  uint32_t seg_cap;
+  const uint32_t* dst_index;
+  void* y_seg[9];
 };
 
 cudaError_t launch_gemv(GemvParams p, int bits, bool moe, uint32_t tokens, uint32_t slots, int sm_count,
@@ -56,11 +64,17 @@ size_t moe_grouped_scratch_bytes(uint32_t experts, uint32_t pairs);
 bool moe_grouped_supported(int bits, uint32_t group, uint32_t K, uint32_t N, uint32_t experts);
 cudaError_t launch_moe_grouped(const GemvParams& g, uint32_t tokens, uint32_t slots, uint32_t* scratch, uint32_t* status,
                                cudaStream_t st);
+// The same contract with the dequantised expert weights as the A operand in tensor memory, persistent over the units
+// (ztvm_moe_ta.cu): the default tensor-core form; launch_moe_grouped stays selectable for comparison.
+bool moe_ta_supported(int bits, uint32_t group, uint32_t K, uint32_t N, uint32_t experts);
+cudaError_t launch_moe_ta(const GemvParams& g, uint32_t tokens, uint32_t slots, uint32_t* scratch, uint32_t* status,
+                          int sm_count, cudaStream_t st, bool reuse_plan = false);
+constexpr uint32_t kMoeTaTileRows = 128, kMoeTcTileRows = 8;   // pairs per tile each kernel asks the plan for
 // Streaming form of the grouped MoE matmul (ztvm_moe_tc.cu) for launches where an expert sees only a few pairs: bound
 // by reading each active expert's weights once. Same scratch as launch_moe_grouped.
 bool moe_tc_supported(const GemvParams& g, int bits);
 cudaError_t launch_moe_tc(const GemvParams& g, uint32_t tokens, uint32_t slots, uint32_t* scratch, int sm_count,
-                          cudaStream_t st);
+                          cudaStream_t st, bool reuse_plan = false);
 // Dispatch plan of the expert-parallel form: pairs in owner-rank order, their local expert index, pairs per rank.
 cudaError_t launch_moe_dispatch_plan(const GemvParams& g, uint32_t tokens, uint32_t slots, uint32_t epr, uint32_t world,
                                      uint32_t* scratch, long long* order, int* local_expert, long long* send_counts,
@@ -71,11 +85,29 @@ bool moe_static_scratch_fits(uint32_t experts, uint64_t pairs);
 cudaError_t launch_moe_grouped_static(const GemvParams& g, uint32_t tokens, uint32_t slots, uint32_t* status,
                                       cudaStream_t st);
 cudaError_t launch_moe_tc_static(const GemvParams& g, uint32_t tokens, uint32_t slots, int sm_count, cudaStream_t st);
+cudaError_t launch_moe_ta_static(const GemvParams& g, uint32_t tokens, uint32_t slots, uint32_t* status, int sm_count,
+                                 cudaStream_t st);
 
 // The same GEMM with the dequantised weights as the A operand in tensor memory and the activations as the only
 // shared-memory operand (ztvm_gemm_ta.cu): the default for M > 8; launch_gemm_w4 stays selectable for comparison.
 cudaError_t launch_gemm_w4_ta(const uint32_t* W, const __half* S, const __half* B, const __half* X, void* Y, uint32_t M,
                               uint32_t N, uint32_t K, uint32_t group_shift, bool out_f32, uint32_t* status, cudaStream_t st);
+
+// Dispatch step of the expert-parallel MoE block (ztvm_moe_ep.cu): pair rows stored straight into the owners' receive
+// buffers (peer-mapped addresses), one region per source rank.
+struct EpDispatchParams {
+  const uint32_t* ids;      // [tokens][ids_stride], first top_k entries of a row are the routed experts
+  const __half* x;          // [tokens][x_tok_stride]
+  uint32_t tokens, top_k, has_shared, ids_stride, slots_total, d, x_tok_stride;
+  uint32_t epr, world, rank, seg_cap;
+  __half* recv_x[8];
+  uint32_t* recv_ids[8];
+  uint32_t* recv_src[8];
+  uint32_t* recv_cnt[8];
+  uint32_t* cursors;        // this rank's own: world + 2 words, zero before the first step
+  uint32_t* err;
+};
+cudaError_t launch_moe_ep_dispatch(const EpDispatchParams& p, int sm_count, cudaStream_t st);
 
 cudaError_t launch_unpack_codes(const uint32_t* W, uint8_t* codes, uint32_t N, uint32_t K, int bits, cudaStream_t st);
 // The codes as the streaming matrix-unit kernels consume them (in-place f16 subnormals, scaled back to integers).
@@ -85,7 +117,9 @@ cudaError_t launch_dequant(const uint32_t* W, const __half* S, const __half* B, 
 
 cudaError_t launch_route_topk(const float* logits, uint32_t* ids, float* scores, uint32_t tokens, uint32_t E,
                               uint32_t K, bool norm_topk, bool has_shared, cudaStream_t st);
-cudaError_t launch_silu_mul(const __half* gate_up, __half* h, uint32_t rows, uint32_t ffn, cudaStream_t st);
+// seg_counts != nullptr: rows come in regions of seg_cap, only the first seg_counts[region] of each are computed
+cudaError_t launch_silu_mul(const __half* gate_up, __half* h, uint32_t rows, uint32_t ffn, cudaStream_t st,
+                            const uint32_t* seg_counts = nullptr, uint32_t seg_cap = 1);
 cudaError_t launch_moe_combine(const __half* y_slots, const float* scores, __half* out, uint32_t tokens,
                                uint32_t slots, uint32_t d, cudaStream_t st);
 

@@ -23,10 +23,18 @@ constexpr int kMoeWorkWarps = 8;
 constexpr int kMoeThreads = 64 + kMoeWorkWarps * 32;
 constexpr int kMoeBM = 128, kMoeBN = 128;
 
+// Entry i of a segmented id list is live when it lies in the filled prefix of its region (expert-parallel form).
+struct MoeSegs {
+  const uint32_t* counts;
+  uint32_t cap;
+  __device__ __forceinline__ bool live(uint32_t i) const { return !counts || (i % cap) < counts[i / cap]; }
+};
+
 __global__ void moe_count_kernel(const uint32_t* __restrict__ ids, uint32_t tokens, uint32_t slots, uint32_t ids_stride,
-                                 uint32_t E, MoeScratch sc, uint32_t* err) {
+                                 uint32_t E, MoeScratch sc, uint32_t* err, MoeSegs segs) {
   const uint32_t P = tokens * slots;
   for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < P; i += gridDim.x * blockDim.x) {
+    if (!segs.live(i)) continue;
     const uint32_t t = i / slots, s = i - t * slots;
     const uint32_t e = ids[(size_t)t * ids_stride + s];
     if (e < E) atomicAdd(&sc.counts[e], 1u);
@@ -83,13 +91,14 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(uint32_t E, uint32_t til
 // The whole plan in ONE block for short pair lists: histogram and cursors in shared memory, same scans, same tables.
 __global__ void __launch_bounds__(1024) moe_plan_small_kernel(const uint32_t* __restrict__ ids, uint32_t tokens, uint32_t slots,
                                                               uint32_t ids_stride, uint32_t E, uint32_t tile_rows,
-                                                              MoeScratch sc, uint32_t* err) {
+                                                              MoeScratch sc, uint32_t* err, MoeSegs segs) {
   __shared__ uint32_t cnt_sm[1024], cur_sm[1024], warp_sums[32];
   const uint32_t e = threadIdx.x, P = tokens * slots;
   cnt_sm[e] = 0u;
   __syncthreads();
   uint32_t bad = 0;
   for (uint32_t i = threadIdx.x; i < P; i += blockDim.x) {
+    if (!segs.live(i)) continue;
     const uint32_t t = i / slots, s = i - t * slots;
     const uint32_t x = ids[(size_t)t * ids_stride + s];
     if (x < E) atomicAdd(&cnt_sm[x], 1u);
@@ -113,6 +122,7 @@ __global__ void __launch_bounds__(1024) moe_plan_small_kernel(const uint32_t* __
   }
   __syncthreads();
   for (uint32_t i = threadIdx.x; i < P; i += blockDim.x) {
+    if (!segs.live(i)) continue;
     const uint32_t t = i / slots, s = i - t * slots;
     const uint32_t x = ids[(size_t)t * ids_stride + s];
     if (x < E) sc.sorted[atomicAdd(&cur_sm[x], 1u)] = i;
@@ -120,9 +130,10 @@ __global__ void __launch_bounds__(1024) moe_plan_small_kernel(const uint32_t* __
 }
 
 __global__ void moe_scatter_kernel(const uint32_t* __restrict__ ids, uint32_t tokens, uint32_t slots,
-                                   uint32_t ids_stride, uint32_t E, MoeScratch sc) {
+                                   uint32_t ids_stride, uint32_t E, MoeScratch sc, MoeSegs segs) {
   const uint32_t P = tokens * slots;
   for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < P; i += gridDim.x * blockDim.x) {
+    if (!segs.live(i)) continue;
     const uint32_t t = i / slots, s = i - t * slots;
     const uint32_t e = ids[(size_t)t * ids_stride + s];
     if (e < E) sc.sorted[sc.offsets[e] + atomicAdd(&sc.cursor[e], 1u)] = i;
@@ -289,12 +300,12 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_w, const MoeGemmPara
       if (ok) issue_a(kn); else asm volatile("cp.async.commit_group;" ::: "memory");
       if (ok) {
         const unsigned short s16 = __ldg(srow + kb), b16 = __ldg(brow + kb);   // group 64: one group per k block
-        const float sf = __half2float(__ushort_as_half(s16)), bf = __half2float(__ushort_as_half(b16));
+        const DqGroup dq = dq_group<true>(s16, b16);
         uint8_t* rowp = gen_base + L::kOffB + s * L::kBBytes + row_off;
         const uint32_t words[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
         for (int wi = 0; wi < 4; ++wi) {
-          const uint4 v = dequant_word_w16<true>(words[wi], s16, sf, bf);
+          const uint4 v = dequant_word_w16<true>(words[wi], dq);
           *reinterpret_cast<uint4*>(rowp + (((part * 4 + wi) ^ (r_tile & 7)) << 4)) = v;
         }
       }
@@ -357,16 +368,17 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_w, const MoeGemmPara
 cudaError_t launch_moe_plan(const GemvParams& g, uint32_t tokens, uint32_t slots, const MoeScratch& sc, uint32_t tile_rows,
                             cudaStream_t st) {
   const uint32_t P = tokens * slots, E = g.experts;
-  if (P <= 4096) {   // short lists: one block does it all, nothing to clear beforehand
-    moe_plan_small_kernel<<<1, 1024, 0, st>>>(g.ids, tokens, slots, g.ids_stride, E, tile_rows, sc, g.err_counter);
+  const MoeSegs segs{g.seg_counts, g.seg_cap ? g.seg_cap : 1u};
+  if (P <= 32768) {   // short lists: one block does it all, nothing to clear beforehand
+    moe_plan_small_kernel<<<1, 1024, 0, st>>>(g.ids, tokens, slots, g.ids_stride, E, tile_rows, sc, g.err_counter, segs);
     return cudaGetLastError();
   }
   cudaError_t e = cudaMemsetAsync(sc.counts, 0, ((size_t)E * 3 + 4) * 4, st);   // counts, offsets, cursor, ntiles
   if (e != cudaSuccess) return e;
   const unsigned blocks = (P + 255) / 256 > 1184 ? 1184 : (P + 255) / 256;
-  moe_count_kernel<<<blocks, 256, 0, st>>>(g.ids, tokens, slots, g.ids_stride, E, sc, g.err_counter);
+  moe_count_kernel<<<blocks, 256, 0, st>>>(g.ids, tokens, slots, g.ids_stride, E, sc, g.err_counter, segs);
   moe_plan_kernel<<<1, 1024, 0, st>>>(E, tile_rows, sc);
-  moe_scatter_kernel<<<blocks, 256, 0, st>>>(g.ids, tokens, slots, g.ids_stride, E, sc);
+  moe_scatter_kernel<<<blocks, 256, 0, st>>>(g.ids, tokens, slots, g.ids_stride, E, sc, segs);
   return cudaGetLastError();
 }
 
@@ -510,6 +522,15 @@ cudaError_t launch_moe_grouped_static(const GemvParams& g, uint32_t tokens, uint
   // launch_moe_grouped zeroes the words that must start at zero (counts, offsets, cursors, tile count) on `st`
   // before the planning kernels; the rest of the scratch is fully written before it is read.
   return launch_moe_grouped(g, tokens, slots, scratch, status, st);
+}
+
+cudaError_t launch_moe_ta_static(const GemvParams& g, uint32_t tokens, uint32_t slots, uint32_t* status, int sm_count,
+                                 cudaStream_t st) {
+  if (!moe_static_scratch_fits(g.experts, (uint64_t)tokens * slots)) return cudaErrorInvalidValue;
+  uint32_t* scratch = nullptr;
+  const cudaError_t e = moe_static_scratch_ptr(&scratch);
+  if (e != cudaSuccess) return e;
+  return launch_moe_ta(g, tokens, slots, scratch, status, sm_count, st);   // its plan launch clears what must start at zero
 }
 
 cudaError_t launch_moe_tc_static(const GemvParams& g, uint32_t tokens, uint32_t slots, int sm_count, cudaStream_t st) {

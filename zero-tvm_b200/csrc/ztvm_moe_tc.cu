@@ -215,10 +215,10 @@ bool moe_tc_supported(const GemvParams& g, int bits) {
 }
 
 cudaError_t launch_moe_tc(const GemvParams& g, uint32_t tokens, uint32_t slots, uint32_t* scratch, int sm_count,
-                          cudaStream_t st) {
+                          cudaStream_t st, bool reuse_plan) {
   const uint32_t P = tokens * slots;
   MoeScratch sc = moe_scratch_carve(scratch, g.experts, P);
-  cudaError_t e = launch_moe_plan(g, tokens, slots, sc, 8u, st);
+  cudaError_t e = reuse_plan ? cudaSuccess : launch_moe_plan(g, tokens, slots, sc, kMoeTcTileRows, st);
   if (e != cudaSuccess) return e;
   MoeTcParams p;
   p.W = g.W; p.S = g.S; p.B = g.B; p.X = g.X; p.Y = reinterpret_cast<__half*>(g.Y);

@@ -103,6 +103,16 @@ class CudaKernels:
         self.be.dispatch(ent_d, [y_slots, h, down[1], down[0], moe_down_pod_args(d, ffn, slots), down[2], ids],
                          (d // 4, tokens, slots), stream=st)
 
+    # -- expert-parallel step without the host in it (rows travel by peer stores; see ExpertParallelMoE) ------------
+    def ep_dispatch(self, layout, ids, tokens, top_k, x, d):
+        self.be.ctx.moe_ep_dispatch(layout, ids, tokens, top_k, True, ids.stride(0), x, d, x.stride(0), stream=self._stream())
+
+    def ep_matmul(self, desc, rows, y, x, stack, ids):
+        self.be.ctx.int4_matmul_moe_ep(desc, rows, y, x, stack[1], stack[0], stack[2], ids, stream=self._stream())
+
+    def ep_silu(self, rows, ffn, h, gu):
+        self.be.ctx.silu_mul_rows(rows, ffn, h, gu, stream=self._stream())
+
     def dense_ffn(self, x, gate, up, down, e, d, ffn, rows):
         """down_e(silu(gate_e x) * up_e x) for every row of x with ONE expert e of the stacks: plain projections."""
         dev = x.device
@@ -228,20 +238,27 @@ def plan_dispatch(ids_routed: torch.Tensor, experts_per_rank: int, world: int, g
 class ExpertParallelMoE:
     """Expert-parallel form of the block the engine runs as seven dispatches (engine-core.ts:2342-2349)."""
 
-    def __init__(self, kernels, gate, up, down, *, E: int, top_k: int, d: int, ffn: int, group=None, max_tokens=None):
-        """gate / up / down: (W, scales, biases) stacks of THIS rank: E/G routed experts followed by the shared one."""
+    def __init__(self, kernels, gate, up, down, *, E: int, top_k: int, d: int, ffn: int, group=None, max_tokens=None,
+                 peer: bool = True, world: int | None = None, rank: int | None = None):
+        """gate / up / down: (W, scales, biases) stacks of THIS rank: E/G routed experts followed by the shared one.
+        world / rank: only to stand in for a process group (tests that run several ranks' steps from one process)."""
         self.k, self.group = kernels, group
-        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
-        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.world = world if world is not None else (dist.get_world_size(group) if dist.is_initialized() else 1)
+        self.rank = rank if rank is not None else (dist.get_rank(group) if dist.is_initialized() else 0)
         assert E % self.world == 0
         self.E, self.top_k, self.d, self.ffn = E, top_k, d, ffn
         self.epr = E // self.world
         self.gate, self.up, self.down = gate, up, down
         self.max_tokens = max_tokens
         # One rank: there is nothing to dispatch, the block is the engine's own sequence of dispatches over the id list.
-        self.form = "one rank: router, gate, up, SiLU, down, combine over the id list" if self.world == 1 else \
-            "NCCL all-to-all of counts, rows and results (host reads the split sizes)"
-        self.capturable = self.world == 1      # no host round trip inside a step
+        # Several ranks, CUDA kernels: rows travel by peer stores from inside the kernels (symmetric memory), counts stay
+        # on the device. Otherwise (CPU ranks of the tests, or peer=False): two all-to-alls with host-read split sizes.
+        self.peer = bool(peer) and self.world > 1 and hasattr(kernels, "ep_dispatch")
+        self.form = ("one rank: router, gate, up, SiLU, down, combine over the id list" if self.world == 1 else
+                     "peer stores: dispatch kernel -> barrier -> grouped expert matmuls over the receive buffer, the down "
+                     "projection storing each result row to its source rank -> barrier -> combine" if self.peer else
+                     "all-to-all of counts, rows and results (host reads the split sizes)")
+        self.capturable = self.world == 1 or self.peer      # no host round trip inside a step
         self._bufs = {}
 
     def _local_block(self, x: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
@@ -261,6 +278,93 @@ class ExpertParallelMoE:
         self.k.combine(b["out"], b["y"], b["scores"], T, K + 1, d)
         return b["out"]
 
+    def peer_bytes(self, T: int):
+        """Size and offsets of one rank's symmetric allocation for T local tokens."""
+        G, K, d = self.world, self.top_k, self.d
+        cap = max(T * K, T)
+        R = (G + 1) * cap
+        al = lambda n: (n + 255) // 256 * 256
+        off_x, off_ids = 0, al(R * d * 2)
+        off_src = off_ids + al(R * 4)
+        off_cnt = off_src + al(R * 4)
+        off_y = off_cnt + 256
+        return off_y + al(T * (K + 1) * d * 2), (off_x, off_ids, off_src, off_cnt, off_y), cap, R
+
+    def _peer_state(self, T: int, dev, buf=None, ptrs=None):
+        """Symmetric receive buffers + result slots for T local tokens (one allocation, one rendezvous).
+        buf / ptrs: an allocation made by the caller and every rank's base address (tests without a process group)."""
+        if ("peer", T) in self._bufs:
+            return self._bufs[("peer", T)]
+        from .capi import MoeDesc, MmDesc, MoeEpLayout, MoeEpRows
+        G, K, d, ffn = self.world, self.top_k, self.d, self.ffn
+        total, (off_x, off_ids, off_src, off_cnt, off_y), cap, R = self.peer_bytes(T)
+        regions = G + 1
+        hdl = None
+        if buf is None:
+            import torch.distributed._symmetric_memory as symm
+            buf = symm.empty((total,), dtype=torch.uint8, device=dev)
+            buf.zero_()
+            g = self.group if self.group is not None else dist.group.WORLD
+            hdl = symm.rendezvous(buf, g.group_name)
+            ptrs = [int(p) for p in hdl.buffer_ptrs]
+        st = dict(hdl=hdl, buf=buf, cap=cap, R=R)
+        view = lambda off, n, dt, shape: buf[off:off + n].view(dt).view(shape)
+        st["recv_x"] = view(off_x, R * d * 2, torch.float16, (R, d))
+        st["recv_ids"] = view(off_ids, R * 4, torch.int32, (R,))
+        st["recv_src"] = view(off_src, R * 4, torch.int32, (R,))
+        st["recv_cnt"] = view(off_cnt, 64, torch.int32, (16,))
+        st["y_slots"] = view(off_y, T * (K + 1) * d * 2, torch.float16, (T, K + 1, d))
+        L = MoeEpLayout()
+        L.world, L.rank, L.experts_per_rank, L.seg_cap = G, self.rank, self.epr, cap
+        for r in range(G):
+            L.recv_x[r], L.recv_ids[r], L.recv_src[r], L.recv_cnt[r] = ptrs[r] + off_x, ptrs[r] + off_ids, ptrs[r] + off_src, ptrs[r] + off_cnt
+        st["cursors"] = torch.zeros((G + 2,), dtype=torch.int32, device=dev)
+        L.cursors = st["cursors"].data_ptr()
+        st["layout"] = L
+
+        def rows(dst: bool, reuse: bool):
+            r = MoeEpRows()
+            r.seg_counts, r.seg_cap, r.segments, r.reuse_plan = st["recv_cnt"].data_ptr(), cap, regions, int(reuse)
+            if dst:
+                r.dst_index = st["recv_src"].data_ptr()
+                for i in range(G):
+                    r.y_seg[i] = ptrs[i] + off_y
+                r.y_seg[G] = ptrs[self.rank] + off_y          # the local region's rows belong to this rank's own tokens
+            return r
+        st["rows_first"], st["rows_again"], st["rows_down"] = rows(False, False), rows(False, True), rows(True, True)
+        mm = lambda Kd, N: MmDesc(Kd, N, 1, 64, 4, 1, 0)
+        E1 = self.epr + 1
+        st["desc_gu"] = MoeDesc(mm(d, ffn), E1, 1, R, 0, 2 * ffn, d, 2 * ffn, 1)
+        st["desc_down"] = MoeDesc(mm(ffn, d), E1, 1, R, 0, d, ffn, d, 1)
+        st["ids"] = torch.empty((T, K + 1), dtype=torch.int32, device=dev)
+        st["scores"] = torch.empty((T, K + 1), dtype=torch.float32, device=dev)
+        st["gu"] = torch.empty((R, 2 * ffn), dtype=torch.float16, device=dev)
+        st["h"] = torch.empty((R, ffn), dtype=torch.float16, device=dev)
+        st["out"] = torch.empty((T, d), dtype=torch.float16, device=dev)
+        self._bufs[("peer", T)] = st
+        return st
+
+    def _peer_block(self, x: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
+        """One step with no host round trip: every launch below is ordered on the current stream, the two barriers are
+        device-side (symmetric-memory signal pads), so the whole step can be replayed from a CUDA graph."""
+        T, K, d, ffn = x.shape[0], self.top_k, self.d, self.ffn
+        st = self._peer_state(T, x.device)
+        self.k.route_topk(st["ids"], st["scores"], logits, self.E, K, T)
+        self.k.ep_dispatch(st["layout"], st["ids"], T, K, x, d)
+        st["hdl"].barrier(channel=0)                   # every rank's rows and counts have landed here
+        self._peer_ffn(st)
+        st["hdl"].barrier(channel=1)                   # every result row is back where its token lives
+        self.k.combine(st["out"], st["y_slots"], st["scores"], T, K + 1, d)
+        return st["out"]
+
+    def _peer_ffn(self, st):
+        """Expert FFN over everything that arrived; the down projection returns each row to its source rank."""
+        ffn = self.ffn
+        self.k.ep_matmul(st["desc_gu"], st["rows_first"], st["gu"], st["recv_x"], self.gate, st["recv_ids"])
+        self.k.ep_matmul(st["desc_gu"], st["rows_again"], st["gu"].view(-1)[ffn:], st["recv_x"], self.up, st["recv_ids"])
+        self.k.ep_silu(st["rows_first"], ffn, st["h"], st["gu"])
+        self.k.ep_matmul(st["desc_down"], st["rows_down"], st["y_slots"], st["h"], self.down, st["recv_ids"])
+
     def _a2a(self, send: torch.Tensor, send_counts, recv_counts) -> torch.Tensor:
         out = torch.empty((sum(recv_counts),) + tuple(send.shape[1:]), dtype=send.dtype, device=send.device)
         if self.world == 1:
@@ -273,12 +377,17 @@ class ExpertParallelMoE:
         """x f16 [T_local, d], logits f32 [T_local, E+1] -> y f16 [T_local, d] (overwritten by the next forward)."""
         if self.world == 1:
             return self._local_block(x, logits)
+        if self.peer:
+            return self._peer_block(x, logits)
         T, K, d = x.shape[0], self.top_k, self.d
         dev = x.device
         ids = torch.empty((T, K + 1), dtype=torch.int32, device=dev)
         scores = torch.empty((T, K + 1), dtype=torch.float32, device=dev)
         self.k.route_topk(ids, scores, logits, self.E, K, T)
         plan = plan_dispatch(ids[:, :K], self.epr, self.world, self.group, kernels=self.k)
+        # ids outside the expert range are left out by the device-side plan: only the filled prefix is a plan
+        n_sent = sum(plan.send_counts)
+        plan.order, plan.local_expert = plan.order[:n_sent], plan.local_expert[:n_sent]
         # dispatch: activation rows and their local expert index, in destination order
         tok_of_pair = torch.div(plan.order, K, rounding_mode="floor")
         x_send = x.index_select(0, tok_of_pair)
@@ -291,7 +400,7 @@ class ExpertParallelMoE:
         # combine: results travel back and are un-permuted into [T, K+1, d]
         y_back = self._a2a(y_recv, plan.recv_counts, plan.send_counts)
         y_slots = torch.empty((T, K + 1, d), dtype=torch.float16, device=dev)
-        routed = torch.empty((T * K, d), dtype=torch.float16, device=dev)
+        routed = torch.zeros((T * K, d), dtype=torch.float16, device=dev)     # a dropped pair contributes nothing
         routed.index_copy_(0, plan.order, y_back)
         y_slots[:, :K] = routed.view(T, K, d)
         # the shared expert is replicated and sees every local token: three dense projections (GEMM / GEMV by T), no ids
