@@ -407,10 +407,12 @@ class ShardedBench:
             fw = [tuple(a.cpu().numpy().view(np.uint32) if a.dtype == torch.int32 else a.cpu().numpy() for a in st) for st in full]
             ref = zo.moe_block(x[:ns].cpu().numpy(), logits[:ns].cpu().numpy(), fw[0], fw[1], fw[2], E, top_k, ffn)["y"]
             got = out[:ns].float().cpu().numpy()
-            err = zo.rel_err_scaled(got, ref.astype(np.float64), 1e-2)
-            verified = {"tokens_checked": ns, "max_rel_err": err, "max_rel_err_pure": zo.rel_err(got, ref.astype(np.float64)),
-                        "tolerance": 4e-3, "note": "whole block (three chained matmuls with f16 stores between) against the oracle's block; floor 1e-2 rms",
-                        "ok": bool(err <= 4e-3 and np.abs(got).max() > 0)}
+            ref64 = ref.astype(np.float64)
+            err = float(np.abs(got - ref64).max() / np.abs(ref64).max())
+            verified = {"tokens_checked": ns, "max_err_over_max_ref": err, "max_rel_err_pure": zo.rel_err(got, ref64),
+                        "tolerance": 5e-3, "note": "whole block (router, three chained expert matmuls with f16 stores between, "
+                        "combine) against the oracle's block; the reference's own whole-block bound, max|y - ref| <= 0.005 max|ref|",
+                        "ok": bool(err <= 5e-3 and np.abs(got).max() > 0)}
             del fw
         del full
 

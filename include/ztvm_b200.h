@@ -132,6 +132,14 @@ ZTVM_API ztvm_status ztvm_int4_matmul_moe(ztvm_ctx* ctx, const ztvm_moe_desc* de
                                  const void* scales, const void* packed_w, const void* biases,
                                  const uint32_t* ids, void* stream);
 
+/* The gate, up and down matmuls of one step walk the same id list, and each ztvm_int4_matmul_moe call sorts it by
+ * expert again (the plan). With reuse enabled, a call whose ids address, tokens, slots, ids_stride and expert count
+ * equal the previous call's uses that call's plan. The caller then promises that the id list changes only through
+ * ztvm_moe_route_topk on this context (which drops the plan), or calls this function again after writing it by other
+ * means (every call drops the plan). Off by default. The reference has no counterpart: its kernels read ids directly
+ * (int4_matmul.gen.ts:229-254) and re-stream an expert's weights per pair. */
+ZTVM_API ztvm_status ztvm_moe_plan_reuse(ztvm_ctx* ctx, int32_t enable);
+
 /* ztvm_int4_matmul_moe for callers that must not let the call allocate. It has no counterpart in the reference
  * (WebGPU buffers are all created up front there); it exists for hosts whose device memory is entirely handed
  * to their own pool, or whose serving loop cannot take the device-wide synchronisation that growing a work

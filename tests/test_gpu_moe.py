@@ -242,6 +242,42 @@ def test_tensor_memory_tiles_on_ragged_shapes(T, E, d, ffn, slots, dev, oracle_c
     be.close()
 
 
+def test_plan_reuse_across_the_matmuls_of_one_step(backend, dev, oracle_c):
+    """With ztvm_moe_plan_reuse on, gate / up / down over one id list build the expert-sorted plan once: same bits as
+    without it; a new id list written by the router at the same address must not meet the old plan."""
+    import torch
+    mb = z.synth.moe_block(64, E=16, hidden=512, ffn=256, seed=61)
+    slots = 5
+    gw, gs, gb = (dev.put(a) for a in mb["gate"])
+    uw, us, ub = (dev.put(a) for a in mb["up"])
+    x = dev.put(mb["x"])
+    logits = [dev.put(mb["logits"]), dev.put(np.ascontiguousarray(mb["logits"][::-1]))]
+    ids = dev.empty((64, slots), np.uint32, fill=0)
+    scores = dev.empty((64, slots), np.float32, fill=0.0)
+    desc = z.MoeDesc(z.MmDesc(512, 256, 1, 64, 4, 1, 0), 17, slots, 64, 0, 256, 512, slots * 256, slots)
+    outs = {}
+    for reuse in (False, True):
+        backend.ctx.moe_plan_reuse(reuse)
+        for li in (0, 1):                       # the second routing overwrites ids in place
+            backend.moe_router_topk(ids, scores, logits[li], 16, 4, True, True, 64)
+            yg = dev.empty((64, slots, 256), np.float16, fill=3.0)
+            yu = dev.empty((64, slots, 256), np.float16, fill=3.0)
+            backend.ctx.int4_matmul_moe(desc, yg, x, gs, gw, gb, ids)
+            backend.ctx.int4_matmul_moe(desc, yu, x, us, uw, ub, ids)
+            outs[(reuse, li)] = (dev.get(yg).view(np.uint16), dev.get(yu).view(np.uint16), dev.get(ids, np.uint32).copy())
+    backend.ctx.moe_plan_reuse(False)
+    assert backend.ctx.device_errors() == 0
+    for li in (0, 1):
+        assert np.array_equal(outs[(False, li)][0], outs[(True, li)][0])
+        assert np.array_equal(outs[(False, li)][1], outs[(True, li)][1])
+        idn = outs[(True, li)][2]
+        ref = oracle_c.moe_matmul_f64(mb["x"], *mb["up"], idn, 256, 512, 64, 4, in_per_slot=False, w16=False)
+        err = zo.rel_err_scaled(outs[(True, li)][1].view(np.float16), ref, 1e-3)
+        record_parity(err, zo.rel_err(outs[(True, li)][1].view(np.float16), ref))
+        assert err <= TOL
+    assert not np.array_equal(outs[(True, 0)][2], outs[(True, 1)][2])
+
+
 def test_moe_argument_errors(backend, dev):
     mb = z.synth.moe_block(2, E=8, hidden=256, ffn=128, seed=1)
     gw, gs, gb = (dev.put(a) for a in mb["gate"])

@@ -16,7 +16,7 @@ LIB_PATH = os.environ.get("ZTVM_LIB") or os.path.join(_HERE, "lib", "libztvm_b20
 SYMBOLS = [
     "ztvm_version", "ztvm_status_string", "ztvm_init", "ztvm_destroy", "ztvm_last_error", "ztvm_sync",
     "ztvm_int4_matmul", "ztvm_int4_matmul_multi", "ztvm_int4_matmul_host", "ztvm_int4_matmul_moe", "ztvm_int4_matmul_moe_noalloc",
-    "ztvm_moe_route_topk", "ztvm_moe_dispatch_plan", "ztvm_moe_ep_dispatch", "ztvm_int4_matmul_moe_ep", "ztvm_silu_mul_rows",
+    "ztvm_moe_plan_reuse", "ztvm_moe_route_topk", "ztvm_moe_dispatch_plan", "ztvm_moe_ep_dispatch", "ztvm_int4_matmul_moe_ep", "ztvm_silu_mul_rows",
     "ztvm_silu_mul",
     "ztvm_moe_combine", "ztvm_unpack_codes", "ztvm_unpack_codes_streamed", "ztvm_dequant", "ztvm_device_errors",
 ]
@@ -80,6 +80,7 @@ def load() -> C.CDLL:
         "ztvm_int4_matmul_host": [vp, C.POINTER(MmDesc), vp, vp, vp, vp, vp],
         "ztvm_int4_matmul_moe": [vp, C.POINTER(MoeDesc), vp, vp, vp, vp, vp, vp, vp],
         "ztvm_int4_matmul_moe_noalloc": [vp, C.POINTER(MoeDesc), vp, vp, vp, vp, vp, vp, vp],
+        "ztvm_moe_plan_reuse": [vp, i32],
         "ztvm_moe_route_topk": [vp, u32, u32, u32, u32, u32, vp, vp, vp, vp],
         "ztvm_moe_dispatch_plan": [vp, vp, u32, u32, u32, u32, u32, u32, vp, vp, vp, vp],
         "ztvm_moe_ep_dispatch": [vp, C.POINTER(MoeEpLayout), vp, u32, u32, u32, u32, vp, u32, u32, vp],
@@ -174,6 +175,10 @@ class Context:
         """The grouped MoE matmul with its plan in a fixed device array (no allocation; limits in the header)."""
         check(self._lib.ztvm_int4_matmul_moe_noalloc(self.handle, C.byref(desc), ptr(y), ptr(x), ptr(scales),
                                                      ptr(packed_w), ptr(biases), ptr(ids), stream_ptr(stream)))
+
+    def moe_plan_reuse(self, enable: bool):
+        """Consecutive int4_matmul_moe calls over one id list share its expert-sorted plan (see the header's contract)."""
+        check(self._lib.ztvm_moe_plan_reuse(self.handle, int(enable)))
 
     def moe_route_topk(self, E, K, norm_topk, has_shared, tokens, ids, scores, logits, stream=None):
         check(self._lib.ztvm_moe_route_topk(self.handle, E, K, int(norm_topk), int(has_shared), tokens, ptr(ids),

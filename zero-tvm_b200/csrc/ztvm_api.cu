@@ -32,7 +32,8 @@ struct ztvm_ctx {
   int moe_grouped;
   int gemm_sm;      // env ZTVM_GEMM=sm: the GEMM with both operands in shared memory (a measurement knob)
   // what the plan in d_ws was built from (ztvm_int4_matmul_moe_ep reuse_plan)
-  const void* plan_ids; const void* plan_segs; uint32_t plan_tokens, plan_tile_rows, plan_experts;
+  const void* plan_ids; const void* plan_segs; uint32_t plan_tokens, plan_tile_rows, plan_experts, plan_slots, plan_stride;
+  int plan_reuse;   // ztvm_moe_plan_reuse: consecutive ztvm_int4_matmul_moe calls over one id list share its plan
   int moe_tiles_sm; // env ZTVM_MOE_TILES=sm: the grouped MoE tiles with both operands in shared memory (a measurement knob)
 };
 
@@ -385,12 +386,19 @@ ztvm_status ztvm_int4_matmul_moe(ztvm_ctx* ctx, const ztvm_moe_desc* md, void* y
       if (ctx->d_ws_bytes < need) {
         ZTVM_CUDA(cudaDeviceSynchronize());
         if ((s = grow(&ctx->d_ws, &ctx->d_ws_bytes, need, false))) return s;
+        ctx->plan_ids = nullptr;
       }
-      ctx->plan_ids = nullptr;      // the plan buffer is rebuilt below: nothing to reuse from an earlier call
       uint32_t* ws = static_cast<uint32_t*>(ctx->d_ws);
-      if (pick == 2) ZTVM_CUDA(ztvm::launch_moe_tc(p, md->tokens, md->slots, ws, ctx->sm_count, st));
-      else if (pick == 1) ZTVM_CUDA(ztvm::launch_moe_ta(p, md->tokens, md->slots, ws, ctx->err_counter + 1, ctx->sm_count, st));
+      const uint32_t tile_rows = pick == 2 ? ztvm::kMoeTcTileRows : ztvm::kMoeTaTileRows;
+      // gate, up and down of one step walk the same id list: with ztvm_moe_plan_reuse on, its plan is built once
+      const bool reuse = ctx->plan_reuse && pick != 3 && ctx->plan_ids == ids && ctx->plan_segs == nullptr &&
+                         ctx->plan_tokens == md->tokens && ctx->plan_slots == md->slots && ctx->plan_stride == md->ids_stride &&
+                         ctx->plan_tile_rows == tile_rows && ctx->plan_experts == md->experts;
+      if (pick == 2) ZTVM_CUDA(ztvm::launch_moe_tc(p, md->tokens, md->slots, ws, ctx->sm_count, st, reuse));
+      else if (pick == 1) ZTVM_CUDA(ztvm::launch_moe_ta(p, md->tokens, md->slots, ws, ctx->err_counter + 1, ctx->sm_count, st, reuse));
       else ZTVM_CUDA(ztvm::launch_moe_grouped(p, md->tokens, md->slots, ws, ctx->err_counter + 1, st));
+      ctx->plan_ids = pick != 3 ? ids : nullptr; ctx->plan_segs = nullptr; ctx->plan_tokens = md->tokens; ctx->plan_slots = md->slots;
+      ctx->plan_stride = md->ids_stride; ctx->plan_tile_rows = tile_rows; ctx->plan_experts = md->experts;
       return ZTVM_OK;
     }
   }
@@ -450,6 +458,14 @@ ztvm_status ztvm_int4_matmul_moe_noalloc(ztvm_ctx* ctx, const ztvm_moe_desc* md,
   return ZTVM_OK;
 }
 
+ztvm_status ztvm_moe_plan_reuse(ztvm_ctx* ctx, int32_t enable) {
+  ztvm_status s = check_ctx(ctx);
+  if (s) return s;
+  ctx->plan_reuse = enable ? 1 : 0;
+  ctx->plan_ids = nullptr;
+  return ZTVM_OK;
+}
+
 ztvm_status ztvm_moe_route_topk(ztvm_ctx* ctx, uint32_t E, uint32_t K, uint32_t norm_topk, uint32_t has_shared,
                                 uint32_t tokens, uint32_t* ids, float* scores, const float* logits, void* stream) {
   ztvm_status s = check_ctx(ctx);
@@ -459,6 +475,7 @@ ztvm_status ztvm_moe_route_topk(ztvm_ctx* ctx, uint32_t E, uint32_t K, uint32_t 
   if (K == 0 || K > 32 || K > E) return fail(ZTVM_ERR_BAD_DIMS, "K=%u: need 1 <= K <= min(32, E)", K);
   if (tokens == 0) return ZTVM_OK;
   cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : ctx->stream;
+  ctx->plan_ids = nullptr;   // a new id list: whatever plan the context holds describes the old one
   ZTVM_CUDA(ztvm::launch_route_topk(logits, ids, scores, tokens, E, K, norm_topk != 0, has_shared != 0, st));
   return ZTVM_OK;
 }
@@ -576,8 +593,8 @@ ztvm_status ztvm_int4_matmul_moe_ep(ztvm_ctx* ctx, const ztvm_moe_desc* md, cons
   uint32_t* ws = static_cast<uint32_t*>(ctx->d_ws);
   if (pick == 2) ZTVM_CUDA(ztvm::launch_moe_tc(p, md->tokens, 1, ws, ctx->sm_count, st, reuse));
   else ZTVM_CUDA(ztvm::launch_moe_ta(p, md->tokens, 1, ws, ctx->err_counter + 1, ctx->sm_count, st, reuse));
-  ctx->plan_ids = ids; ctx->plan_segs = rows->seg_counts; ctx->plan_tokens = md->tokens;
-  ctx->plan_tile_rows = tile_rows; ctx->plan_experts = md->experts;
+  ctx->plan_ids = ids; ctx->plan_segs = rows->seg_counts; ctx->plan_tokens = md->tokens; ctx->plan_slots = 1;
+  ctx->plan_stride = md->ids_stride; ctx->plan_tile_rows = tile_rows; ctx->plan_experts = md->experts;
   return ZTVM_OK;
 }
 

@@ -239,44 +239,96 @@ cudaError_t launch_route_topk(const float* logits, uint32_t* ids, float* scores,
 
 // ---- SiLU * up -----------------------------------------------------------------------------------
 // Rows of [gate(ffn) | up(ffn)] f16 -> f16 [ffn]; f32 arithmetic (silu_mul.wgsl:40-43).
+__device__ __forceinline__ float silu_mul_one(float g, float u) {
+  const float sg = g * (1.0f / (1.0f + expf(-g)));
+  return u * sg;
+}
+// VEC = 8: eight elements per thread (16-byte loads and stores; ffn % 8 == 0, 16-byte aligned buffers), else one.
+template <int VEC>
 __global__ void silu_mul_kernel(const __half* __restrict__ gate_up, __half* __restrict__ h, uint32_t rows, uint32_t ffn,
                                 const uint32_t* __restrict__ seg_counts, uint32_t seg_cap) {
-  const size_t total = (size_t)rows * ffn;
+  const uint32_t per_row = ffn / VEC;
+  const size_t total = (size_t)rows * per_row;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-    const size_t r = i / ffn, c = i - r * ffn;
+    const size_t r = i / per_row, c = (i - r * per_row) * VEC;
     if (seg_counts && (uint32_t)(r % seg_cap) >= seg_counts[r / seg_cap]) continue;   // past the region's live rows
-    const float g = __half2float(gate_up[r * 2 * ffn + c]);
-    const float u = __half2float(gate_up[r * 2 * ffn + ffn + c]);
-    const float sg = g * (1.0f / (1.0f + expf(-g)));
-    h[i] = __float2half_rn(u * sg);
+    if constexpr (VEC == 8) {
+      const uint4 gv = *reinterpret_cast<const uint4*>(gate_up + r * 2 * ffn + c);
+      const uint4 uv = *reinterpret_cast<const uint4*>(gate_up + r * 2 * ffn + ffn + c);
+      const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
+      uint32_t ow[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 g2 = __half22float2(u32_as_h2(gw[k])), u2 = __half22float2(u32_as_h2(uw[k]));
+        const __half2 o = __floats2half2_rn(silu_mul_one(g2.x, u2.x), silu_mul_one(g2.y, u2.y));
+        ow[k] = *reinterpret_cast<const uint32_t*>(&o);
+      }
+      *reinterpret_cast<uint4*>(h + r * ffn + c) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    } else {
+      const float g = __half2float(gate_up[r * 2 * ffn + c]);
+      const float u = __half2float(gate_up[r * 2 * ffn + ffn + c]);
+      h[r * ffn + c] = __float2half_rn(silu_mul_one(g, u));
+    }
   }
 }
 cudaError_t launch_silu_mul(const __half* gate_up, __half* h, uint32_t rows, uint32_t ffn, cudaStream_t st,
                             const uint32_t* seg_counts, uint32_t seg_cap) {
   const size_t total = (size_t)rows * ffn;
   if (total == 0) return cudaSuccess;
-  silu_mul_kernel<<<grid_for(total, 256), 256, 0, st>>>(gate_up, h, rows, ffn, seg_counts, seg_cap ? seg_cap : 1u);
+  const bool vec = ffn % 8 == 0 && ((reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(h)) & 15u) == 0;
+  if (vec) silu_mul_kernel<8><<<grid_for(total / 8, 256), 256, 0, st>>>(gate_up, h, rows, ffn, seg_counts, seg_cap ? seg_cap : 1u);
+  else silu_mul_kernel<1><<<grid_for(total, 256), 256, 0, st>>>(gate_up, h, rows, ffn, seg_counts, seg_cap ? seg_cap : 1u);
   return cudaGetLastError();
 }
 
 // ---- weighted combine -----------------------------------------------------------------------------
 // out[t][i] = f16(sum_s score[t][s] * f32(y[t][s][i])), slots added in index order (moe_combine.wgsl:39-43).
+template <int VEC>
 __global__ void moe_combine_kernel(const __half* __restrict__ y, const float* __restrict__ scores, __half* __restrict__ out,
                                    uint32_t tokens, uint32_t slots, uint32_t d) {
-  const size_t total = (size_t)tokens * d;
+  const uint32_t per_row = d / VEC;
+  const size_t total = (size_t)tokens * per_row;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-    const size_t t = i / d, c = i - t * d;
-    float acc = 0.f;
-    for (uint32_t s = 0; s < slots; ++s)
-      acc = __fadd_rn(acc, __fmul_rn(scores[t * slots + s], __half2float(y[(t * slots + s) * d + c])));
-    out[i] = __float2half_rn(acc);
+    const size_t t = i / per_row, c = (i - t * per_row) * VEC;
+    float acc[VEC];
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) acc[k] = 0.f;
+    for (uint32_t s = 0; s < slots; ++s) {
+      const float sc = scores[t * slots + s];
+      const __half* src = y + (t * slots + s) * d + c;
+      if constexpr (VEC == 8) {
+        const uint4 v = *reinterpret_cast<const uint4*>(src);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 f = __half22float2(u32_as_h2(w[k]));
+          acc[2 * k] = __fadd_rn(acc[2 * k], __fmul_rn(sc, f.x));
+          acc[2 * k + 1] = __fadd_rn(acc[2 * k + 1], __fmul_rn(sc, f.y));
+        }
+      } else {
+        acc[0] = __fadd_rn(acc[0], __fmul_rn(sc, __half2float(src[0])));
+      }
+    }
+    if constexpr (VEC == 8) {
+      uint32_t ow[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const __half2 o = __floats2half2_rn(acc[2 * k], acc[2 * k + 1]);
+        ow[k] = *reinterpret_cast<const uint32_t*>(&o);
+      }
+      *reinterpret_cast<uint4*>(out + t * d + c) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    } else {
+      out[t * d + c] = __float2half_rn(acc[0]);
+    }
   }
 }
 cudaError_t launch_moe_combine(const __half* y_slots, const float* scores, __half* out, uint32_t tokens,
                                uint32_t slots, uint32_t d, cudaStream_t st) {
   const size_t total = (size_t)tokens * d;
   if (total == 0) return cudaSuccess;
-  moe_combine_kernel<<<grid_for(total, 256), 256, 0, st>>>(y_slots, scores, out, tokens, slots, d);
+  const bool vec = d % 8 == 0 && ((reinterpret_cast<uintptr_t>(y_slots) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0;
+  if (vec) moe_combine_kernel<8><<<grid_for(total / 8, 256), 256, 0, st>>>(y_slots, scores, out, tokens, slots, d);
+  else moe_combine_kernel<1><<<grid_for(total, 256), 256, 0, st>>>(y_slots, scores, out, tokens, slots, d);
   return cudaGetLastError();
 }
 

@@ -88,21 +88,53 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(uint32_t E, uint32_t til
   }
 }
 
-// The whole plan in ONE block for short pair lists: histogram and cursors in shared memory, same scans, same tables.
+// Increment of cnt[key] by every active lane, returning the lane's slot. When all active lanes of the warp hold the
+// same key (the slot of a shared expert: thousands of pairs with one id), one lane adds for the warp; one atomic per
+// pair on that single address would serialise the whole plan. Mixed keys take one atomic per lane (little contention).
+__device__ __forceinline__ uint32_t moe_agg_add(uint32_t* cnt, uint32_t key, bool active) {
+  const uint32_t amask = __ballot_sync(0xffffffffu, active);
+  if (amask == 0u) return 0u;
+  const int lane = threadIdx.x & 31, leader = __ffs(amask) - 1;
+  const uint32_t key0 = __shfl_sync(0xffffffffu, key, leader);
+  const bool uniform = __all_sync(0xffffffffu, !active || key == key0);
+  if (uniform) {
+    uint32_t base = 0u;
+    if (lane == leader) base = atomicAdd(&cnt[key0], (uint32_t)__popc(amask));
+    base = __shfl_sync(0xffffffffu, base, leader);
+    return base + (uint32_t)__popc(amask & ((1u << lane) - 1u));
+  }
+  return active ? atomicAdd(&cnt[key], 1u) : 0u;
+}
+
+// The whole plan in ONE block for pair lists up to a few tens of thousands: histogram and cursors in shared memory,
+// same scans, same tables. Pairs are walked slot-major (a warp sees 32 tokens of one slot), so the pairs of a slot
+// that always carries the same expert (the shared expert) aggregate into one atomic per warp.
+constexpr uint32_t kPlanSmallMax = 32768;   // pairs the one-block plan takes: 32 per thread, kept in registers
 __global__ void __launch_bounds__(1024) moe_plan_small_kernel(const uint32_t* __restrict__ ids, uint32_t tokens, uint32_t slots,
                                                               uint32_t ids_stride, uint32_t E, uint32_t tile_rows,
                                                               MoeScratch sc, uint32_t* err, MoeSegs segs) {
   __shared__ uint32_t cnt_sm[1024], cur_sm[1024], warp_sums[32];
   const uint32_t e = threadIdx.x, P = tokens * slots;
   cnt_sm[e] = 0u;
+  // every id of this thread is loaded up front (independent loads in flight together), then counted, then scattered
+  uint32_t xs[kPlanSmallMax / 1024];
+#pragma unroll
+  for (int k = 0; k < (int)(kPlanSmallMax / 1024); ++k) {
+    const uint32_t j = threadIdx.x + 1024u * k;                     // j = slot * tokens + token
+    xs[k] = 0xFFFFFFFFu;
+    if (j < P) {
+      const uint32_t s = j / tokens, t = j - s * tokens;
+      if (segs.live(t * slots + s)) xs[k] = ids[(size_t)t * ids_stride + s];
+      else xs[k] = 0xFFFFFFFEu;                                    // not a pair at all (past a region's live rows)
+    }
+  }
   __syncthreads();
   uint32_t bad = 0;
-  for (uint32_t i = threadIdx.x; i < P; i += blockDim.x) {
-    if (!segs.live(i)) continue;
-    const uint32_t t = i / slots, s = i - t * slots;
-    const uint32_t x = ids[(size_t)t * ids_stride + s];
-    if (x < E) atomicAdd(&cnt_sm[x], 1u);
-    else ++bad;
+#pragma unroll
+  for (int k = 0; k < (int)(kPlanSmallMax / 1024); ++k) {
+    if (1024u * k >= P) break;                                      // block-uniform
+    if (xs[k] >= E && xs[k] < 0xFFFFFFFEu) ++bad;
+    moe_agg_add(cnt_sm, xs[k], xs[k] < E);
   }
   if (bad) atomicAdd(err, bad);
   __syncthreads();
@@ -121,11 +153,16 @@ __global__ void __launch_bounds__(1024) moe_plan_small_kernel(const uint32_t* __
     tt[2] = min(tile_rows, cnt - j * tile_rows);
   }
   __syncthreads();
-  for (uint32_t i = threadIdx.x; i < P; i += blockDim.x) {
-    if (!segs.live(i)) continue;
-    const uint32_t t = i / slots, s = i - t * slots;
-    const uint32_t x = ids[(size_t)t * ids_stride + s];
-    if (x < E) sc.sorted[atomicAdd(&cur_sm[x], 1u)] = i;
+#pragma unroll
+  for (int k = 0; k < (int)(kPlanSmallMax / 1024); ++k) {
+    if (1024u * k >= P) break;
+    const uint32_t j = threadIdx.x + 1024u * k;
+    const bool ok = xs[k] < E;
+    const uint32_t pos = moe_agg_add(cur_sm, xs[k], ok);
+    if (ok) {
+      const uint32_t s = j / tokens, t = j - s * tokens;
+      sc.sorted[pos] = t * slots + s;
+    }
   }
 }
 
@@ -369,7 +406,7 @@ cudaError_t launch_moe_plan(const GemvParams& g, uint32_t tokens, uint32_t slots
                             cudaStream_t st) {
   const uint32_t P = tokens * slots, E = g.experts;
   const MoeSegs segs{g.seg_counts, g.seg_cap ? g.seg_cap : 1u};
-  if (P <= 32768) {   // short lists: one block does it all, nothing to clear beforehand
+  if (P <= kPlanSmallMax) {   // short lists: one block does it all, nothing to clear beforehand
     moe_plan_small_kernel<<<1, 1024, 0, st>>>(g.ids, tokens, slots, g.ids_stride, E, tile_rows, sc, g.err_counter, segs);
     return cudaGetLastError();
   }

@@ -44,9 +44,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_
 #pragma unroll 1
     for (int i = 0; i < 32; ++i) {
       if (mbar_try_wait(bar, parity)) return true;
-#ifndef ZTVM_NO_WAIT_SLEEP
       __nanosleep(40);
-#endif
     }
     if (*abort_flag) return false;
     if ((unsigned long long)(clock64() - t0) > kWaitCycles) {

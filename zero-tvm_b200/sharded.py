@@ -97,11 +97,16 @@ class CudaKernels:
         ent_g = resolve_matmul(affine=True, K=d, moe=True)
         ent_d = resolve_matmul(affine=True, K=ffn, moe=True)
         grid = (ffn // 4, tokens, slots)
-        self.be.dispatch(ent_g, [gu, x, gate[1], gate[0], moe_gate_pod_args(d, ffn, slots), gate[2], ids], grid, stream=st)
-        self.be.dispatch(ent_g, [gu.view(-1)[ffn:], x, up[1], up[0], moe_gate_pod_args(d, ffn, slots), up[2], ids], grid, stream=st)
-        self.be.silu_mul(h, gu, tokens * slots, ffn, stream=st)
-        self.be.dispatch(ent_d, [y_slots, h, down[1], down[0], moe_down_pod_args(d, ffn, slots), down[2], ids],
-                         (d // 4, tokens, slots), stream=st)
+        # the three matmuls walk one id list, which nothing writes in between: its expert-sorted plan is built once
+        self.be.ctx.moe_plan_reuse(True)
+        try:
+            self.be.dispatch(ent_g, [gu, x, gate[1], gate[0], moe_gate_pod_args(d, ffn, slots), gate[2], ids], grid, stream=st)
+            self.be.dispatch(ent_g, [gu.view(-1)[ffn:], x, up[1], up[0], moe_gate_pod_args(d, ffn, slots), up[2], ids], grid, stream=st)
+            self.be.silu_mul(h, gu, tokens * slots, ffn, stream=st)
+            self.be.dispatch(ent_d, [y_slots, h, down[1], down[0], moe_down_pod_args(d, ffn, slots), down[2], ids],
+                             (d // 4, tokens, slots), stream=st)
+        finally:
+            self.be.ctx.moe_plan_reuse(False)
 
     # -- expert-parallel step without the host in it (rows travel by peer stores; see ExpertParallelMoE) ------------
     def ep_dispatch(self, layout, ids, tokens, top_k, x, d):
