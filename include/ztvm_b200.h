@@ -78,12 +78,14 @@ typedef struct ztvm_mm_desc {
   uint32_t N;       /* output features (weight rows) */
   uint32_t M;       /* activation rows (1 = decode) */
   uint32_t group;   /* 64 (MLX affine) or 32 (MLC symmetric) */
-  uint32_t bits;    /* 4 or 3 */
+  uint32_t bits;    /* 4, 3 or 8 (8: K_PACKED = K/4, affine only: the int8_affine_* family) */
   uint32_t affine;  /* 1: w = scale*q + bias   0: w = scale*(q-7), biases ignored */
   uint32_t out_f32; /* 1: y is f32 (lm_head), 0: f16 */
 } ztvm_mm_desc;
 
-/* y = x * dequant(W)^T. Replaces every dispatch of an int4_matmul* pipeline on a dense projection:
+/* y = x * dequant(W)^T. Replaces every dispatch of an int4_matmul* pipeline on a dense projection (and, with
+ * bits = 8, int8_affine_matvec / int8_affine_batched, src/compiler/shaders/int8_affine_matvec.wgsl,
+ * int8_affine_batched.wgsl; selected at src/zero-tvm/variants.ts:370-388):
  * int4_matmul[_f32][_sg|_tiled|_tiled8][_vec4|_vec4h][_affine][_q3], int4_matmul_batched_m4,
  * int4_matmul_batched_dyn[_affine] and the tiled / subgroup-matrix prefill GEMMs
  * (src/compiler/shaders/int4_matmul.gen.ts:170-571, :580-695, :805-1456; call sites
@@ -162,6 +164,25 @@ ZTVM_API ztvm_status ztvm_moe_plan_reuse(ztvm_ctx* ctx, int32_t enable);
 ZTVM_API ztvm_status ztvm_int4_matmul_moe_noalloc(ztvm_ctx* ctx, const ztvm_moe_desc* desc, void* y, const void* x,
                                          const void* scales, const void* packed_w, const void* biases,
                                          const uint32_t* ids, void* stream);
+
+/* Router logits: logits f32[tokens][rows] = x f16[tokens][D] * router^T, rows = experts (+ the shared expert's gate row).
+ * bits 8 / 4: affine group-64 router (w u32[rows][D*bits/32], scales / biases f16[rows][D/64]); bits 16: w f16[rows][D],
+ * scales / biases ignored. Replaces moe_router_logits, moe_router_logits_q4 (src/compiler/shaders/moe_router_logits.wgsl:44-140)
+ * and moe_router_logits_f16 (moe_router_logits_f16.wgsl); bind group [logits, x, w, scales, biases, {D, rows}], grid
+ * (rows, tokens) (src/zero-tvm/engine-core.ts:2031-2033, :2331, :4383). f32 accumulation over exact codes at every token
+ * count (the logits feed a softmax and a top-k). */
+ZTVM_API ztvm_status ztvm_moe_router_logits(ztvm_ctx* ctx, uint32_t D, uint32_t rows, uint32_t tokens, uint32_t bits,
+                                   float* logits, const void* x, const void* w, const void* scales, const void* biases,
+                                   void* stream);
+
+/* Embedding rows of an affine-quantised table: out f16[seq_len][D], row t = dequantised row input_ids[t] of weights
+ * u32[vocab][D*bits/32] with scales / biases f16[vocab][D/64]; bits 4 or 8. The values are the canonical f16 weights
+ * (f16_rne(fl32(s*q + b)), what ztvm_dequant gives). Replaces embedding_affine (src/compiler/shaders/embedding_affine.wgsl:38-57)
+ * and embedding_affine_int8 (embedding_affine_int8.wgsl); bind group [out, input_ids, scales, weights, {seq_len, ..}, biases].
+ * An id outside [0, vocab) leaves its row untouched and is counted (ztvm_device_errors). */
+ZTVM_API ztvm_status ztvm_embedding_affine(ztvm_ctx* ctx, uint32_t D, uint32_t bits, uint32_t vocab, uint32_t seq_len, void* out,
+                                  const int32_t* input_ids, const void* scales, const void* weights, const void* biases,
+                                  void* stream);
 
 /* softmax over E routed experts -> top-K (ties to the lower index) -> optional renormalisation ->
  * slot K = expert E with sigmoid(logit[E]) when has_shared. logits f32[tokens][E+has_shared] ->

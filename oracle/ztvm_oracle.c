@@ -67,6 +67,8 @@ static inline void block_codes(const uint32_t* row, long blk, int bits, float q[
   if (bits == 4) {
     uint32_t p = row[blk];
     for (int i = 0; i < 8; ++i) q[i] = (float)((p >> (4 * i)) & 15u);
+  } else if (bits == 8) { /* four bytes per word (int8_affine_matvec.wgsl: (word >> 8n) & 255) */
+    for (int i = 0; i < 8; ++i) q[i] = (float)((row[2 * blk + (i >> 2)] >> (8 * (i & 3))) & 255u);
   } else {
     uint32_t w = window3(row, blk);
     for (int i = 0; i < 8; ++i) q[i] = (float)((w >> (3 * i)) & 7u);

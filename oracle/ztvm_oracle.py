@@ -62,11 +62,13 @@ def pack_codes(q: np.ndarray, bits: int) -> np.ndarray:
         q32 = q.reshape(*lead, K // 8, 8).astype(np.uint32)
         shifts = (np.arange(8, dtype=np.uint32) * 4)
         return (q32 << shifts).sum(axis=-1, dtype=np.uint32)
+    if bits == 8:   # four bytes per word, little end first (int8_affine_matvec.wgsl, moe_router_logits.wgsl: word >> 8n)
+        return np.ascontiguousarray(q).view("<u4").reshape(*lead, K // 4)
     if bits == 3:
         b = np.stack([(q >> j) & 1 for j in range(3)], axis=-1).reshape(*lead, K * 3)
         by = np.packbits(b.astype(np.uint8), axis=-1, bitorder="little")
         return np.ascontiguousarray(by).view("<u4").reshape(*lead, K * 3 // 32)
-    raise ValueError("bits must be 3 or 4")
+    raise ValueError("bits must be 3, 4 or 8")
 
 
 def unpack_codes(W: np.ndarray, bits: int) -> np.ndarray:
@@ -81,12 +83,14 @@ def unpack_codes(W: np.ndarray, bits: int) -> np.ndarray:
     if bits == 4:
         shifts = (np.arange(8, dtype=np.uint32) * 4)
         return ((W[..., None] >> shifts) & 15).astype(np.uint8).reshape(*lead, KP * 8)
+    if bits == 8:
+        return W.view(np.uint8).reshape(*lead, KP * 4).copy()
     if bits == 3:
         K = KP * 32 // 3
         bitsarr = np.unpackbits(W.view(np.uint8).reshape(*lead, KP * 4), axis=-1, bitorder="little")
         return (bitsarr[..., 0::3][..., :K] + 2 * bitsarr[..., 1::3][..., :K]
                 + 4 * bitsarr[..., 2::3][..., :K]).astype(np.uint8)
-    raise ValueError("bits must be 3 or 4")
+    raise ValueError("bits must be 3, 4 or 8")
 
 
 def unpack_codes_q3_window(W: np.ndarray) -> np.ndarray:
@@ -228,6 +232,58 @@ def rel_err_scaled(y, y_ref, frac: float = 1e-3) -> float:
     y_ref = np.asarray(y_ref).astype(F64)
     rms = float(np.sqrt(np.mean(y_ref * y_ref))) if y_ref.size else 0.0
     return rel_err(y, y_ref, max(frac * rms, 1e-30))
+
+
+# --------------------------------------------------------------------------
+# router logits and embedding rows
+# --------------------------------------------------------------------------
+def router_logits_f64(x, w, scales=None, biases=None, bits: int = 8) -> np.ndarray:
+    """logits[t, e] as an f64 dot over the dequantised router (f32-exact weights; bits 16: the f16 weights themselves).
+
+    moe_router_logits.wgsl:44-140 / run.mjs:186-283: logit = sum_g (s_g * sum x q + b_g * sum x), q unsigned, no offset;
+    moe_router_logits_f16.wgsl: plain f16 weights. x f16 [T, D] -> f64 [T, rows].
+    """
+    x = np.atleast_2d(np.asarray(x, dtype=F16)).astype(F64)
+    if bits == 16:
+        return x @ np.asarray(w, dtype=F16).astype(F64).T
+    q = unpack_codes(w, bits)
+    return x @ dequant_w32(q, scales, biases, 64, True).astype(F64).T
+
+
+def router_logits_word_order_f32(x, w, scales, biases, bits: int) -> np.ndarray:
+    """The shader's own order for one token (moe_router_logits.wgsl:68-99): thread tid of 64 takes words tid, tid+64, ...;
+    per word acc += s*dot + b*xs in f32; then the pairwise tree over the 64 threads. Pure-Python; small cases only."""
+    x = np.asarray(x, dtype=F16).astype(F32).reshape(-1)
+    W = np.asarray(w, dtype=np.uint32)
+    rows, WPR = W.shape
+    per = 32 // bits
+    out = np.zeros(rows, dtype=F32)
+    for e in range(rows):
+        acc = np.zeros(64, dtype=F32)
+        for wi in range(WPR):
+            g = wi * per // 64
+            s_, b_ = F32(np.asarray(scales, dtype=F16)[e, g]), F32(np.asarray(biases, dtype=F16)[e, g])
+            dot, xs = F32(0), F32(0)
+            for n in range(per):
+                v = x[wi * per + n]
+                dot = F32(dot + v * F32((int(W[e, wi]) >> (bits * n)) & ((1 << bits) - 1)))
+                xs = F32(xs + v)
+            t = wi % 64
+            acc[t] = F32(acc[t] + F32(F32(s_ * dot) + F32(b_ * xs)))
+        st = 32
+        while st > 0:
+            acc[:st] = (acc[:st] + acc[st:2 * st]).astype(F32)
+            st //= 2
+        out[e] = acc[0]
+    return out
+
+
+def embedding_rows(input_ids, W, scales, biases, bits: int = 4) -> np.ndarray:
+    """out[t] = dequantised row input_ids[t] as f16 (embedding_affine.wgsl:38-57): the canonical W16 of that row, which is
+    what the reference's real-weights test compares the shader with (tests/kernels/real-weights.mjs:721-750, 0.005)."""
+    ids = np.asarray(input_ids).astype(np.int64)
+    q = unpack_codes(np.asarray(W, dtype=np.uint32)[ids], bits)
+    return dequant_w16(q, np.asarray(scales)[ids], np.asarray(biases)[ids], 64, True)
 
 
 # --------------------------------------------------------------------------
@@ -396,3 +452,32 @@ def reference_test_expected(case) -> np.ndarray:
         b = case["biases"].astype(F64).repeat(case["group"], axis=1)
         return (s * q * x[None] + b * x[None]).sum(axis=1)
     return (s * (q - 7.0) * x[None]).sum(axis=1)
+
+
+def reference_router_case(bits: int, D: int = 2048, rows: int = 9):
+    """Inputs of makeRouterLogitsTest (tests/kernels/run.mjs:199-216), same seed (11 + bits) and draw order: x in
+    [-1, 1), codes uniform, scales in [0.005, 0.025), biases in [-0.1, 0.1); bits 16 draws f16 weights in [-0.05, 0.05)
+    after the (unused) quantised tensors, as the test does. Returns dict(x f16[D], w, scales, biases)."""
+    r = mulberry32(11 + bits)
+    GPR = D // 64
+    maxq = (1 << bits) - 1
+    x = to_f16(np.array([r() * 2 - 1 for _ in range(D)]))
+    q = np.array([int(np.floor(r() * (maxq + 1))) for _ in range(rows * D)], dtype=np.int64).reshape(rows, D)
+    scales = to_f16(np.array([r() * 0.02 + 0.005 for _ in range(rows * GPR)])).reshape(rows, GPR)
+    biases = to_f16(np.array([r() * 0.2 - 0.1 for _ in range(rows * GPR)])).reshape(rows, GPR)
+    if bits == 16:
+        w = to_f16(np.array([r() * 0.1 - 0.05 for _ in range(rows * D)])).reshape(rows, D)
+        return dict(x=x, w=w, bits=16)
+    return dict(x=x, w=pack_codes(q.astype(np.uint8), bits), scales=scales, biases=biases, bits=bits, q=q)
+
+
+def reference_router_expected(case) -> np.ndarray:
+    """The f64 reference of tests/kernels/run.mjs:217-233: per group, scale * dot + bias * xs, accumulated in double."""
+    x = case["x"].astype(F64)
+    if case["bits"] == 16:
+        return case["w"].astype(F64) @ x
+    q = case["q"].astype(F64)
+    rows, D = q.shape
+    xg = x.reshape(D // 64, 64)
+    dot = (q.reshape(rows, D // 64, 64) * xg[None]).sum(axis=2)
+    return (case["scales"].astype(F64) * dot + case["biases"].astype(F64) * xg.sum(axis=1)[None]).sum(axis=1)

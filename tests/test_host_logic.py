@@ -212,3 +212,36 @@ def test_plan_dispatch_uses_a_kernels_hook_when_there_is_one():
     assert Hook.calls == 1 and got.send_counts == ref.send_counts
     assert sorted(got.order.tolist()) == list(range(80))
     assert torch.equal(got.local_expert, (ids.reshape(-1).to(torch.int64)[got.order] % 32).to(torch.int32))
+
+
+def test_chunk_cap_and_gemm_ladder():
+    """resolveChunkCap and pickChunkGemm as the reference's pure functions (src/zero-tvm/engine-core.ts:195-245)."""
+    from zero_tvm_b200.backend import pick_chunk_gemm_ladder, resolve_chunk_cap
+    assert resolve_chunk_cap() == 1024 and resolve_chunk_cap(sgmat_avail=False) == 64
+    assert resolve_chunk_cap(chunk_cap=96) == 96 and resolve_chunk_cap(max_chunk_cap=256) == 256
+    assert resolve_chunk_cap(max_chunk_cap=256, sgmat_avail=False) == 64
+    assert pick_chunk_gemm_ladder() == ("e5", None)
+    assert pick_chunk_gemm_ladder(e5_ready=False) == ("sgmat", None)
+    assert pick_chunk_gemm_ladder(e5_ready=False, sgmat_ready=False) == ("matvec", None)
+    assert pick_chunk_gemm_ladder(cap_tiles64=False) == ("sgmat", None)            # nothing asked for: the ladder applies
+    assert pick_chunk_gemm_ladder(chunk_tiled=True, e5_ready=False, sgmat_ready=False) == ("tiled", None)
+    used, why = pick_chunk_gemm_ladder(want="e5", cap_tiles64=False, cap=96)
+    assert used == "sgmat" and "cap must be %64 (got 96)" in why
+    used, why = pick_chunk_gemm_ladder(want="sgmat", dims_ok=False, cap=1000)
+    assert used == "matvec" and "dims do not tile" in why
+    used, why = pick_chunk_gemm_ladder(want="e5", e5_ready=False)
+    assert used == "sgmat" and "not built" in why
+    assert pick_chunk_gemm_ladder(want="tiled") == ("tiled", None) and pick_chunk_gemm_ladder(want="matvec") == ("matvec", None)
+
+
+def test_resolve_matmul_for_spec_and_int8_entries():
+    from zero_tvm_b200.backend import parse_entry, resolve_matmul_for_spec
+    assert resolve_matmul_for_spec(weight_format="mlx-safetensors", weight_bits=8, K=4096) == "int8_affine_matvec"
+    assert resolve_matmul_for_spec(weight_format="mlx-safetensors", K=4096) == "int4_matmul_sg_tiled_vec4h_affine" or \
+        resolve_matmul_for_spec(weight_format="mlx-safetensors", K=4096).endswith("_affine")
+    assert not resolve_matmul_for_spec(weight_format="mlc", K=4096).endswith("_affine")
+    with pytest.raises(ValueError):
+        resolve_matmul_for_spec(weight_format="mlx-safetensors", weight_bits=8, K=4096, moe=True)
+    for name, m_rows in (("int8_affine_matvec", False), ("int8_affine_batched", True)):
+        info = parse_entry(name)
+        assert info.bits == 8 and info.affine and info.has_m_rows == m_rows and not info.moe

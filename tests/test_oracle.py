@@ -58,7 +58,37 @@ def test_unpack_and_factored_gemv_match_reference_kernel_ref(path, oracle_c):
         assert zo.rel_err_scaled(got, g["y"], 1e-3) <= 2e-3
 
 
-@pytest.mark.parametrize("bits", [4, 3])
+@pytest.mark.parametrize("bits", [16, 8, 4])
+def test_router_logits_reference_case(bits, oracle_c):
+    """The reference's own router test (tests/kernels/run.mjs:186-283: mulberry32 seed 11 + bits, D 2048, 9 rows, its
+    formula in f64) through the oracle: the f64 anchor equals its reference loop, and the shader's word order in f32 sits
+    inside its gate max |got - ref| / (|ref| + 1e-2) < 1e-4."""
+    case = zo.reference_router_case(bits)
+    ref = zo.reference_router_expected(case)
+    y64 = zo.router_logits_f64(case["x"], case["w"], case.get("scales"), case.get("biases"), bits)[0]
+    assert np.max(np.abs(y64 - ref) / (np.abs(ref) + 1e-2)) < 1e-9
+    if bits != 16:
+        got = zo.router_logits_word_order_f32(case["x"], case["w"], case["scales"], case["biases"], bits)
+        assert np.max(np.abs(got - ref) / (np.abs(ref) + 1e-2)) < 1e-4
+        gc = oracle_c.gemv_ref(case["x"].reshape(1, -1), case["w"], case["scales"], case["biases"], 64, bits, True, out_f32=True)[0]
+        assert np.max(np.abs(gc - ref) / (np.abs(ref) + 1e-2)) < 1e-4
+
+
+def test_embedding_rows_are_the_canonical_w16(oracle_c):
+    import zero_tvm_b200 as z
+    for bits in (4, 8):
+        rng = np.random.default_rng(31 + bits)
+        q, W, s, b = z.synth.make_weights(rng, 50, 256, bits=bits)
+        ids = np.array([3, 49, 0, 3, 17], dtype=np.int32)
+        rows = zo.embedding_rows(ids, W, s, b, bits)
+        full = oracle_c.dequant(W, s, b, 64, bits, True, out_f16=True)
+        assert np.array_equal(rows.view(np.uint16), full[ids].view(np.uint16))
+        # f16 arithmetic as the shader writes it (f16(q) * s + b) agrees with it within the reference's 0.005 gate
+        sh = (q[ids].astype(np.float16) * s[ids].repeat(64, 1) + b[ids].repeat(64, 1)).astype(np.float64)
+        assert np.abs(sh - rows.astype(np.float64)).max() <= 0.005 * np.abs(rows.astype(np.float64)).max()
+
+
+@pytest.mark.parametrize("bits", [4, 3, 8])
 def test_pack_unpack_roundtrip(bits, oracle_c):
     rng = np.random.default_rng(5)
     q = rng.integers(0, 1 << bits, size=(7, 448), dtype=np.uint8)
@@ -112,7 +142,7 @@ def test_reference_test_cases(K, flavour, oracle_c):
 
 def test_c_and_numpy_oracles_agree(oracle_c):
     import zero_tvm_b200 as z
-    for bits, group, affine in ((4, 64, True), (3, 64, True), (4, 32, False)):
+    for bits, group, affine in ((4, 64, True), (3, 64, True), (4, 32, False), (8, 64, True)):
         p = z.synth.projection(48, 768, M=3, bits=bits, group=group, affine=affine, seed=9)
         w32 = zo.dequant_w32(p["q"], p["scales"], p["biases"], group, affine)
         assert np.array_equal(oracle_c.dequant(p["W"], p["scales"], p["biases"], group, bits, affine), w32)

@@ -6,6 +6,7 @@ dequant-matmul family, behind a C ABI (include/ztvm_b200.h).
            groups, grids) on top of `capi`
 `synth`    seeded synthetic tensors in the kernels' layouts
 `build`    nvcc build of libztvm_b200.so
+`ingest`   MLX safetensors records -> the buffers the kernels bind (host side, numpy)
 
 There is no CPU implementation: importing is cheap, but creating a Context without the built
 library or without a B200 raises.
@@ -15,3 +16,4 @@ from .capi import Context, MmDesc, MoeDesc, MoeEpLayout, MoeEpRows, ZtvmError  #
 from . import backend  # noqa: F401
 from . import sharded  # noqa: F401,E402
 from . import build  # noqa: F401,E402
+from . import ingest  # noqa: F401,E402

@@ -106,6 +106,11 @@ def parse_entry(entry: str) -> EntryInfo:
     """Decodes what an entry name fixes. Unknown names raise KeyError, as a missing pipeline does."""
     if entry == "int4_matmul_batched_m4":
         return EntryInfo(False, 4, False, False, False, 4)
+    # the 8-bit family (src/compiler/shaders/int8_affine_matvec.wgsl, int8_affine_batched.wgsl): K_PACKED = K / 4
+    if entry == "int8_affine_matvec":
+        return EntryInfo(True, 8, False, False, False, None)
+    if entry == "int8_affine_batched":
+        return EntryInfo(True, 8, False, False, True, None)
     base = entry[:-len("_affine")] if entry.endswith("_affine") else entry
     if base in _GEMM_ENTRIES:
         return EntryInfo(entry.endswith("_affine"), 4, False, False, True, None)
@@ -161,19 +166,71 @@ def resolve_matmul(*, affine: bool, K: int, out_f32: bool = False, subgroups: bo
                                             vec4=(K % 1024 == 0), vec4_half=(K % 1024 != 0 and K % 512 == 0)))
 
 
-def pick_chunk_gemm(requested: Optional[str], *, affine: bool, K: int) -> str:
-    """Prefill GEMM choice (engine-core.ts:220-245): an explicit request that cannot run throws instead of
-    silently falling back; otherwise the matrix-unit GEMM when K % 64 == 0, else the runtime-M matvec."""
+def resolve_matmul_for_spec(*, weight_format: str, weight_bits: int = 4, K: int, out_f32: bool = False, q3: bool = False,
+                            moe: bool = False) -> str:
+    """One matmul instance for one spec (src/zero-tvm/variants.ts:370-388): the 8-bit branch first (an 8-bit checkpoint
+    may never be served by the 4-bit kernels: silent wrong logits), everything else through resolve_matmul with the
+    family decided by the checkpoint format."""
+    if weight_bits == 8:
+        if out_f32 or q3 or moe:
+            raise ValueError("the 8-bit family has one matvec and one batched kernel: no f32-output, 3-bit or MoE twin")
+        return "int8_affine_matvec"
+    return resolve_matmul(affine=weight_format == "mlx-safetensors", K=K, out_f32=out_f32, q3=q3, moe=moe)
+
+
+def resolve_chunk_cap(chunk_cap: Optional[int] = None, max_chunk_cap: Optional[int] = None, sgmat_avail: bool = True) -> int:
+    """Rows per prefill chunk (src/zero-tvm/engine-core.ts:195-202): an explicit option wins; otherwise 1024 when the
+    matrix-unit GEMM is there (it always is here), 64 without it, clamped by the spec's own maximum."""
+    if chunk_cap is not None:
+        return chunk_cap
+    cap = 1024 if sgmat_avail else 64
+    return cap if max_chunk_cap is None else min(cap, max_chunk_cap)
+
+
+_GEMM_NAMES = {"e5": "int4_matmul_sg_e5", "e1": "int4_matmul_sg_e1", "sgmat": "int4_matmul_sgmat",
+               "tiled": "int4_matmul_tiled_st", "matvec": "int4_matmul_batched_dyn"}
+
+
+def pick_chunk_gemm_ladder(*, want: Optional[str] = None, chunk_tiled: bool = False, dims_ok: bool = True,
+                           cap_tiles64: bool = True, e5_ready: bool = True, sgmat_ready: bool = True, cap: int = 1024):
+    """The chunk-prefill GEMM ladder as the reference's pure function (src/zero-tvm/engine-core.ts:220-245):
+    e5 > sgmat > tiled (only when asked for) > matvec. Returns (used, rejected): an EXPLICIT `want` that cannot run is a
+    rejection carrying the throw text, never a silent substitution. All rungs land on the same tcgen05 GEMM here
+    (matvec: the runtime-M GEMV path), so e5_ready / sgmat_ready default to True."""
+    w = want if want is not None else ("e5" if e5_ready else "sgmat" if sgmat_ready else "matvec")
+    ladder = [("e5", w == "e5" and dims_ok and cap_tiles64 and e5_ready),
+              ("sgmat", w in ("sgmat", "e5") and dims_ok and sgmat_ready),
+              ("tiled", (w == "tiled" or chunk_tiled) and dims_ok),
+              ("matvec", True)]
+    used = next(name for name, ok in ladder if ok)
+    if want is not None and used != want:
+        if not dims_ok:
+            why = f"dims do not tile (cap {cap}, d/qDim/ffn must be %64 and cap %32)"
+        elif want == "e5" and not cap_tiles64:
+            why = f"E5 stages a 64-row tile, so cap must be %64 (got {cap})"
+        elif want in ("e5", "sgmat"):
+            why = "its pipeline was not built"
+        else:
+            why = "that pipeline was not built"
+        return used, f"chunkGemm: asked for '{want}', can only run '{used}' — {why}"
+    return used, None
+
+
+def pick_chunk_gemm(requested: Optional[str], *, affine: bool, K: int, cap: int = 1024) -> str:
+    """Entry name of the prefill GEMM for one projection: the ladder above with this projection's K as the tiling
+    condition; a rejected explicit request raises (the reference throws at engine build, engine-core.ts:3969)."""
     suffix = "_affine" if affine else ""
-    names = {"e5": "int4_matmul_sg_e5", "e1": "int4_matmul_sg_e1", "sgmat": "int4_matmul_sgmat",
-             "tiled": "int4_matmul_tiled_st", "matvec": "int4_matmul_batched_dyn"}
-    if requested is not None:
-        if requested not in names:
-            raise ValueError(f"unknown GEMM kernel '{requested}'")
-        if requested != "matvec" and K % 64:
-            raise ValueError(f"GEMM kernel '{requested}' needs K % 64 == 0 (K={K})")
-        return names[requested] + suffix
-    return (names["e5"] if K % 64 == 0 else names["matvec"]) + suffix
+    if requested is not None and requested not in _GEMM_NAMES:
+        raise ValueError(f"unknown GEMM kernel '{requested}'")
+    want = None if requested in (None, "e1") else requested
+    used, rejected = pick_chunk_gemm_ladder(want=want, dims_ok=K % 64 == 0 and cap % 32 == 0, cap_tiles64=cap % 64 == 0, cap=cap)
+    if rejected:
+        raise ValueError(rejected)
+    if requested == "e1":
+        if K % 64:
+            raise ValueError(f"GEMM kernel 'e1' needs K % 64 == 0 (K={K})")
+        used = "e1"
+    return _GEMM_NAMES[used] + suffix
 
 
 # ---- the dispatch surface ---------------------------------------------------------------------------
@@ -237,6 +294,32 @@ class CudaMatmulBackend:
         if hasattr(weights, "nbytes"):
             return int(weights.nbytes // (4 * n * k_packed))
         raise TypeError("MoE weights must be a sized buffer (tensor / array) so the expert count is known")
+
+    # -- the router matvec and the embedding gather (their own bind-group orders in the reference) ---------------------
+    def dispatch_router_logits(self, entry: str, bindings: Sequence, grid: Sequence[int] = (1, 1, 1), stream=None):
+        """moe_router_logits / moe_router_logits_q4: [logits, x, w, scales, biases, {D, rows}]; moe_router_logits_f16:
+        [logits, x, w, {D, rows}] (src/zero-tvm/engine-core.ts:2031-2033). grid = (rows, tokens, 1) (:2331, :4383)."""
+        bits = {"moe_router_logits": 8, "moe_router_logits_q4": 4, "moe_router_logits_f16": 16}.get(entry)
+        if bits is None:
+            raise KeyError(f"no such router pipeline: {entry}")
+        if bits == 16:
+            logits, x, w, pod = bindings[:4]
+            scales = biases = None
+        else:
+            logits, x, w, scales, biases, pod = bindings[:6]
+        D, rows = int(pod[0]), int(pod[1])
+        tokens = int((list(grid) + [1, 1])[1])
+        self.ctx.moe_router_logits(D, rows, tokens, bits, logits, x, w, scales, biases, stream)
+
+    def dispatch_embedding(self, entry: str, bindings: Sequence, D: int, stream=None):
+        """embedding_affine / embedding_affine_int8: [out, input_ids, scales, weights, {seq_len, packGridDimX}, biases]
+        (src/compiler/shaders/embedding_affine.wgsl:20-31); D is a pipeline constant in the reference."""
+        bits = {"embedding_affine": 4, "embedding_affine_int8": 8}.get(entry)
+        if bits is None:
+            raise KeyError(f"no such embedding pipeline: {entry}")
+        out, input_ids, scales, weights, pod, biases = bindings[:6]
+        vocab = self._experts_of(weights, 1, D * bits // 32)
+        self.ctx.embedding_affine(D, bits, vocab, int(pod[0]), out, input_ids, scales, weights, biases, stream)
 
     # MoE glue, same argument order as the reference bind groups
     def moe_router_topk(self, ids, scores, logits, E: int, K: int, norm_topk: bool, has_shared: bool, tokens: int,

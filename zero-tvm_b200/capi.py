@@ -16,7 +16,7 @@ LIB_PATH = os.environ.get("ZTVM_LIB") or os.path.join(_HERE, "lib", "libztvm_b20
 SYMBOLS = [
     "ztvm_version", "ztvm_status_string", "ztvm_init", "ztvm_destroy", "ztvm_last_error", "ztvm_sync",
     "ztvm_int4_matmul", "ztvm_int4_matmul_multi", "ztvm_int4_matmul_host", "ztvm_int4_matmul_moe", "ztvm_int4_matmul_moe_noalloc",
-    "ztvm_moe_plan_reuse", "ztvm_moe_route_topk", "ztvm_moe_dispatch_plan", "ztvm_moe_ep_dispatch", "ztvm_int4_matmul_moe_ep", "ztvm_silu_mul_rows",
+    "ztvm_moe_router_logits", "ztvm_embedding_affine", "ztvm_moe_plan_reuse", "ztvm_moe_route_topk", "ztvm_moe_dispatch_plan", "ztvm_moe_ep_dispatch", "ztvm_int4_matmul_moe_ep", "ztvm_silu_mul_rows",
     "ztvm_silu_mul",
     "ztvm_moe_combine", "ztvm_unpack_codes", "ztvm_unpack_codes_streamed", "ztvm_dequant", "ztvm_device_errors",
 ]
@@ -80,6 +80,8 @@ def load() -> C.CDLL:
         "ztvm_int4_matmul_host": [vp, C.POINTER(MmDesc), vp, vp, vp, vp, vp],
         "ztvm_int4_matmul_moe": [vp, C.POINTER(MoeDesc), vp, vp, vp, vp, vp, vp, vp],
         "ztvm_int4_matmul_moe_noalloc": [vp, C.POINTER(MoeDesc), vp, vp, vp, vp, vp, vp, vp],
+        "ztvm_moe_router_logits": [vp, u32, u32, u32, u32, vp, vp, vp, vp, vp, vp],
+        "ztvm_embedding_affine": [vp, u32, u32, u32, u32, vp, vp, vp, vp, vp, vp],
         "ztvm_moe_plan_reuse": [vp, i32],
         "ztvm_moe_route_topk": [vp, u32, u32, u32, u32, u32, vp, vp, vp, vp],
         "ztvm_moe_dispatch_plan": [vp, vp, u32, u32, u32, u32, u32, u32, vp, vp, vp, vp],
@@ -175,6 +177,14 @@ class Context:
         """The grouped MoE matmul with its plan in a fixed device array (no allocation; limits in the header)."""
         check(self._lib.ztvm_int4_matmul_moe_noalloc(self.handle, C.byref(desc), ptr(y), ptr(x), ptr(scales),
                                                      ptr(packed_w), ptr(biases), ptr(ids), stream_ptr(stream)))
+
+    def moe_router_logits(self, D, rows, tokens, bits, logits, x, w, scales=None, biases=None, stream=None):
+        check(self._lib.ztvm_moe_router_logits(self.handle, D, rows, tokens, bits, ptr(logits), ptr(x), ptr(w), ptr(scales),
+                                               ptr(biases), stream_ptr(stream)))
+
+    def embedding_affine(self, D, bits, vocab, seq_len, out, input_ids, scales, weights, biases, stream=None):
+        check(self._lib.ztvm_embedding_affine(self.handle, D, bits, vocab, seq_len, ptr(out), ptr(input_ids), ptr(scales),
+                                              ptr(weights), ptr(biases), stream_ptr(stream)))
 
     def moe_plan_reuse(self, enable: bool):
         """Consecutive int4_matmul_moe calls over one id list share its expert-sorted plan (see the header's contract)."""

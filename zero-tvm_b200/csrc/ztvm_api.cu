@@ -89,9 +89,10 @@ int log2_exact(uint32_t v) {
 // Layout rules shared by every matmul entry point.
 ztvm_status check_desc(const ztvm_mm_desc* d, bool need_m) {
   if (!d) return fail(ZTVM_ERR_NULL_POINTER, "desc is NULL");
-  if (d->bits != 4 && d->bits != 3) return fail(ZTVM_ERR_UNSUPPORTED, "bits=%u: only 4 and 3 are implemented", d->bits);
-  if (d->bits == 3 && !d->affine)
-    return fail(ZTVM_ERR_UNSUPPORTED, "3-bit weights exist only in the affine layout");
+  if (d->bits != 4 && d->bits != 3 && d->bits != 8)
+    return fail(ZTVM_ERR_UNSUPPORTED, "bits=%u: 8, 4 and 3 are implemented", d->bits);
+  if (d->bits != 4 && !d->affine)
+    return fail(ZTVM_ERR_UNSUPPORTED, "%u-bit weights exist only in the affine layout", d->bits);
   const int gs = log2_exact(d->group);
   if (gs < 5 || gs > 8) return fail(ZTVM_ERR_BAD_DIMS, "group=%u: must be a power of two in [32, 256]", d->group);
   if (d->K == 0 || d->N == 0) return fail(ZTVM_ERR_BAD_DIMS, "K=%u N=%u: must be non-zero", d->K, d->N);
@@ -268,6 +269,50 @@ ztvm_status ztvm_int4_matmul(ztvm_ctx* ctx, const ztvm_mm_desc* d, void* y, cons
   return ZTVM_OK;
 }
 
+// One router logit per (token, row): the exact-code GEMV in slabs of eight tokens for quantised routers (never the f16
+// tensor-core GEMM: logits feed a softmax and a top-k, so they keep the f32-accumulated exact-code arithmetic of the
+// reference's matvec whatever the token count), a plain f16 matvec for routers stored in f16.
+ztvm_status ztvm_moe_router_logits(ztvm_ctx* ctx, uint32_t D, uint32_t rows, uint32_t tokens, uint32_t bits, float* logits,
+                                   const void* x, const void* w, const void* scales, const void* biases, void* stream) {
+  ztvm_status s = check_ctx(ctx);
+  if (s) return s;
+  if (!logits || !x || !w) return fail(ZTVM_ERR_NULL_POINTER, "logits/x/w must be non-NULL");
+  if (D == 0 || rows == 0) return fail(ZTVM_ERR_BAD_DIMS, "D=%u rows=%u: must be non-zero", D, rows);
+  if (tokens == 0) return ZTVM_OK;
+  cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : ctx->stream;
+  if (bits == 16) {
+    if (!aligned(x, 16) || !aligned(w, 16) || D % 8) return fail(ZTVM_ERR_ALIGNMENT, "f16 router: x and w 16-byte aligned, D %% 8 == 0");
+    ZTVM_CUDA(ztvm::launch_f16_matvec(static_cast<const __half*>(x), static_cast<const __half*>(w), logits, D, rows, tokens, st));
+    return ZTVM_OK;
+  }
+  if (bits != 8 && bits != 4) return fail(ZTVM_ERR_UNSUPPORTED, "router bits=%u: 16, 8 and 4 are implemented", bits);
+  ztvm_mm_desc d = {D, rows, tokens, 64, bits, 1, 1};
+  if ((s = check_desc(&d, true))) return s;
+  if ((s = check_buffers(&d, logits, x, scales, w, biases))) return s;
+  const int keep = ctx->no_gemm;
+  ctx->no_gemm = 1;
+  s = ztvm_int4_matmul(ctx, &d, logits, x, scales, w, biases, st);
+  ctx->no_gemm = keep;
+  return s;
+}
+
+ztvm_status ztvm_embedding_affine(ztvm_ctx* ctx, uint32_t D, uint32_t bits, uint32_t vocab, uint32_t seq_len, void* out,
+                                  const int32_t* input_ids, const void* scales, const void* weights, const void* biases,
+                                  void* stream) {
+  ztvm_status s = check_ctx(ctx);
+  if (s) return s;
+  if (!out || !input_ids || !scales || !weights || !biases) return fail(ZTVM_ERR_NULL_POINTER, "out/input_ids/scales/weights/biases must be non-NULL");
+  if (bits != 4 && bits != 8) return fail(ZTVM_ERR_UNSUPPORTED, "embedding bits=%u: 4 and 8 are implemented", bits);
+  if (D == 0 || D % 64 || vocab == 0) return fail(ZTVM_ERR_BAD_DIMS, "D=%u must be a non-zero multiple of the group size 64, vocab=%u non-zero", D, vocab);
+  if (!aligned(out, 16) || !aligned(weights, 4)) return fail(ZTVM_ERR_ALIGNMENT, "out must be 16-byte aligned");
+  if (seq_len == 0) return ZTVM_OK;
+  cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : ctx->stream;
+  ZTVM_CUDA(ztvm::launch_embedding_affine(input_ids, static_cast<const uint32_t*>(weights), static_cast<const __half*>(scales),
+                                          static_cast<const __half*>(biases), static_cast<__half*>(out), seq_len, D, vocab,
+                                          (int)bits, ctx->err_counter, st));
+  return ZTVM_OK;
+}
+
 ztvm_status ztvm_int4_matmul_multi(ztvm_ctx* ctx, const ztvm_mm_desc* d, void* const* y_dsts, uint32_t n_dst,
                                    uint32_t y_row_stride, const void* x, const void* scales, const void* packed_w,
                                    const void* biases, void* stream) {
@@ -360,6 +405,7 @@ ztvm_status ztvm_int4_matmul_moe(ztvm_ctx* ctx, const ztvm_moe_desc* md, void* y
   const ztvm_mm_desc* d = &md->mm;
   if ((s = check_desc(d, false))) return s;
   if (!d->affine) return fail(ZTVM_ERR_UNSUPPORTED, "MoE expert weights are affine-quantised only");
+  if (d->bits == 8) return fail(ZTVM_ERR_UNSUPPORTED, "MoE expert weights are 4-bit or 3-bit");
   if (d->out_f32) return fail(ZTVM_ERR_UNSUPPORTED, "MoE expert matmuls write f16");
   if (d->M > 1) return fail(ZTVM_ERR_BAD_DIMS, "MoE matmul is per (token, slot): mm.M must be 1 (or 0)");
   if ((s = check_buffers(d, y, x, scales, packed_w, biases))) return s;
@@ -651,6 +697,7 @@ ztvm_status ztvm_unpack_codes_streamed(ztvm_ctx* ctx, const ztvm_mm_desc* d, uin
   if ((s = check_desc(d, false))) return s;
   if (!codes || !packed_w) return fail(ZTVM_ERR_NULL_POINTER, "codes/packed_w must be non-NULL");
   if (!aligned(codes, 8) || !aligned(packed_w, 4)) return fail(ZTVM_ERR_ALIGNMENT, "codes need 8-byte alignment");
+  if (d->bits == 8) return fail(ZTVM_ERR_UNSUPPORTED, "8-bit weights have no streaming matrix-unit kernel: use ztvm_unpack_codes");
   if (d->bits == 3 && d->K % 64) return fail(ZTVM_ERR_BAD_DIMS, "3-bit streams are unpacked per 64 codes: K=%u", d->K);
   cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : ctx->stream;
   ZTVM_CUDA(ztvm::launch_unpack_codes_streamed(static_cast<const uint32_t*>(packed_w), codes, d->N, d->K, (int)d->bits, st));

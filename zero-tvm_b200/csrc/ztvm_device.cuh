@@ -86,6 +86,17 @@ __device__ __forceinline__ void codes4_f32(uint32_t w, float q[8]) {
   q[0] = a.x; q[4] = a.y; q[1] = b.x; q[5] = b.y; q[2] = d.x; q[6] = d.y; q[3] = e.x; q[7] = e.y;
 }
 
+// ---- 8-bit codes ---------------------------------------------------------------------------
+// Four codes per word, code i at bits [8i, 8i+8) (src/compiler/shaders/int8_affine_matvec.wgsl,
+// moe_router_logits.wgsl: `(word >> (8u * n)) & 255u`). A block of eight codes is two words.
+__device__ __forceinline__ void codes8_f32(uint32_t w0, uint32_t w1, float q[8]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    q[i] = (float)((w0 >> (8 * i)) & 255u);
+    q[4 + i] = (float)((w1 >> (8 * i)) & 255u);
+  }
+}
+
 // ---- 3-bit codes ---------------------------------------------------------------------------
 // A row is one LSB-first bitstream; 32 codes occupy exactly three words. Codes 8b..8b+7 of such a
 // triple are the 24-bit window starting at bit 24b.

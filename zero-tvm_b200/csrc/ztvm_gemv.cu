@@ -30,7 +30,7 @@ gemv_kernel(const GemvParams p) {
   extern __shared__ float4 smem_f4[];
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
-  constexpr int WPU = BITS;  // words per 32-code unit: 4 bits -> 4, 3 bits -> 3
+  constexpr int WPU = BITS;  // words per 32-code unit: 8 bits -> 8, 4 bits -> 4, 3 bits -> 3
 
   const uint32_t* __restrict__ W = p.W;
   const __half* __restrict__ S = p.S;
@@ -120,6 +120,10 @@ gemv_kernel(const GemvParams p) {
         if constexpr (BITS == 4) {
           const uint4 v = ld_stream_u4(wrow[r] + (size_t)u * 4);
           w[r][0] = v.x; w[r][1] = v.y; w[r][2] = v.z; w[r][3] = v.w;
+        } else if constexpr (BITS == 8) {
+          const uint4 v0 = ld_stream_u4(wrow[r] + (size_t)u * 8), v1 = ld_stream_u4(wrow[r] + (size_t)u * 8 + 4);
+          w[r][0] = v0.x; w[r][1] = v0.y; w[r][2] = v0.z; w[r][3] = v0.w;
+          w[r][4] = v1.x; w[r][5] = v1.y; w[r][6] = v1.z; w[r][7] = v1.w;
         } else {
 #pragma unroll
           for (int k = 0; k < WPU; ++k) w[r][k] = ld_stream_u32(wrow[r] + (size_t)u * 3 + k);
@@ -151,6 +155,7 @@ gemv_kernel(const GemvParams p) {
         for (int r = 0; r < ROWS; ++r) {
           float q[8];
           if constexpr (BITS == 4) codes4_f32(w[r][j], q);
+          else if constexpr (BITS == 8) codes8_f32(w[r][2 * j], w[r][2 * j + 1], q);
           else codes3_f32(window3(w[r][0], w[r][1], w[r][2], j), q);
 #pragma unroll
           for (int m = 0; m < MT; ++m) {
@@ -616,7 +621,7 @@ cudaError_t launch_gemv(GemvParams p, int bits, bool moe, uint32_t tokens, uint3
   int rows = 4;
   while (rows > 1 && ((uint64_t)(p.N + kGemvWarps * rows - 1) / (kGemvWarps * rows)) * pairs < (uint64_t)sm_count * 4)
     rows >>= 1;
-  if (mt == 8 && rows > 2) rows = 2;  // register pressure
+  if ((mt == 8 || bits == 8) && rows > 2) rows = 2;  // register pressure
   const uint32_t units = p.K >> 5;
   uint32_t tile_units = (uint32_t)(kGemvTileElems / mt) >> 5;
   const uint32_t units_up = (units + 31) & ~31u;
@@ -645,6 +650,7 @@ cudaError_t launch_gemv(GemvParams p, int bits, bool moe, uint32_t tokens, uint3
     return launch_rows<3, 1, true>(p, rows, grid, smem, st);
   }
   if (bits == 4) { ZTVM_MT(4, false) }
+  if (bits == 8) { ZTVM_MT(8, false) }
   ZTVM_MT(3, false)
 #undef ZTVM_MT
 }

@@ -14,6 +14,8 @@ __device__ __forceinline__ void load_block_codes(const uint32_t* W, uint32_t KP,
   const uint32_t* row = W + (size_t)n * KP;
   if constexpr (BITS == 4) {
     codes4_f32(row[blk], q);
+  } else if constexpr (BITS == 8) {
+    codes8_f32(row[2 * blk], row[2 * blk + 1], q);
   } else {
     const uint32_t u = blk >> 2, j = blk & 3;
     const uint32_t w0 = row[u * 3], w1 = row[u * 3 + 1], w2 = row[u * 3 + 2];
@@ -136,6 +138,7 @@ static inline unsigned grid_for(size_t total, int block) {
 cudaError_t launch_unpack_codes(const uint32_t* W, uint8_t* codes, uint32_t N, uint32_t K, int bits, cudaStream_t st) {
   const size_t total = (size_t)N * (K >> 3);
   if (bits == 4) unpack_codes_kernel<4><<<grid_for(total, 256), 256, 0, st>>>(W, codes, N, K);
+  else if (bits == 8) unpack_codes_kernel<8><<<grid_for(total, 256), 256, 0, st>>>(W, codes, N, K);
   else unpack_codes_kernel<3><<<grid_for(total, 256), 256, 0, st>>>(W, codes, N, K);
   return cudaGetLastError();
 }
@@ -154,10 +157,103 @@ cudaError_t launch_dequant(const uint32_t* W, const __half* S, const __half* B, 
   if (bits == 4) {
     if (affine) { if (as_f16) ZTVM_DQ(4, true, true); else ZTVM_DQ(4, true, false); }
     else        { if (as_f16) ZTVM_DQ(4, false, true); else ZTVM_DQ(4, false, false); }
+  } else if (bits == 8) {
+    if (as_f16) ZTVM_DQ(8, true, true); else ZTVM_DQ(8, true, false);
   } else {
     if (as_f16) ZTVM_DQ(3, true, true); else ZTVM_DQ(3, true, false);
   }
 #undef ZTVM_DQ
+  return cudaGetLastError();
+}
+
+// ---- embedding rows (embedding_affine.wgsl:38-57, embedding_affine_int8.wgsl) ------------------------------
+// out[t][:] = the dequantised row input_ids[t] of an affine-quantised table, f16: the canonical W16 (what the vendor
+// dequantiser stores), through the same word dequantiser as the GEMMs for 4-bit codes. One thread per 8 values.
+template <int BITS>
+__global__ void embedding_affine_kernel(const int32_t* __restrict__ input_ids, const uint32_t* __restrict__ W,
+                                        const __half* __restrict__ S, const __half* __restrict__ B, __half* __restrict__ out,
+                                        uint32_t seq_len, uint32_t D, uint32_t vocab, uint32_t* err) {
+  const uint32_t nblk = D >> 3, KP = D * BITS / 32, SPR = D >> 6;
+  const size_t total = (size_t)seq_len * nblk;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const uint32_t t = (uint32_t)(i / nblk), blk = (uint32_t)(i - (size_t)t * nblk);
+    const int32_t id = input_ids[t];
+    if (id < 0 || (uint32_t)id >= vocab) {          // counted, the row is left untouched
+      if (blk == 0) atomicAdd(err, 1u);
+      continue;
+    }
+    const size_t n = (size_t)id;
+    const uint32_t g = blk >> 3;
+    const unsigned short s16 = reinterpret_cast<const unsigned short*>(S)[n * SPR + g];
+    const unsigned short b16 = reinterpret_cast<const unsigned short*>(B)[n * SPR + g];
+    uint4 v;
+    if constexpr (BITS == 4) {
+      v = dequant_word_w16<true>(W[n * KP + blk], dq_group<true>(s16, b16));
+    } else {
+      float q[8];
+      codes8_f32(W[n * KP + 2 * blk], W[n * KP + 2 * blk + 1], q);
+      const float sf = __half2float(__ushort_as_half(s16)), bf = __half2float(__ushort_as_half(b16));
+      __half h[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) h[k] = dequant_w16<true>(q[k], sf, bf);
+      v = *reinterpret_cast<uint4*>(h);
+    }
+    *reinterpret_cast<uint4*>(out + (size_t)t * D + (size_t)blk * 8) = v;
+  }
+}
+cudaError_t launch_embedding_affine(const int32_t* input_ids, const uint32_t* W, const __half* S, const __half* B, __half* out,
+                                    uint32_t seq_len, uint32_t D, uint32_t vocab, int bits, uint32_t* err, cudaStream_t st) {
+  const size_t total = (size_t)seq_len * (D >> 3);
+  if (total == 0) return cudaSuccess;
+  if (bits == 4) embedding_affine_kernel<4><<<grid_for(total, 256), 256, 0, st>>>(input_ids, W, S, B, out, seq_len, D, vocab, err);
+  else embedding_affine_kernel<8><<<grid_for(total, 256), 256, 0, st>>>(input_ids, W, S, B, out, seq_len, D, vocab, err);
+  return cudaGetLastError();
+}
+
+// ---- f16 matvec with f32 accumulation and f32 output (moe_router_logits_f16.wgsl) -------------------------------
+// y[t][e] = sum_i f32(x[t][i]) * f32(w[e][i]). One warp per (row e, slab of up to 8 tokens); 16-byte loads.
+__global__ void __launch_bounds__(256) f16_matvec_kernel(const __half* __restrict__ x, const __half* __restrict__ w,
+                                                          float* __restrict__ y, uint32_t D, uint32_t rows, uint32_t tokens) {
+  const uint32_t lane = threadIdx.x & 31u;
+  const uint32_t e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const uint32_t t0 = blockIdx.y * 8u;
+  if (e >= rows) return;
+  const uint32_t nt = min(8u, tokens - t0);
+  float acc[8];
+#pragma unroll
+  for (int m = 0; m < 8; ++m) acc[m] = 0.f;
+  for (uint32_t c = lane; c < D / 8u; c += 32u) {
+    const uint4 wv = __ldg(reinterpret_cast<const uint4*>(w + (size_t)e * D) + c);
+    const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+    for (int m = 0; m < 8; ++m) {
+      if ((uint32_t)m >= nt) break;
+      const uint4 xv = __ldg(reinterpret_cast<const uint4*>(x + (size_t)(t0 + m) * D) + c);
+      const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 a = __half22float2(u32_as_h2(xw[k])), b = __half22float2(u32_as_h2(ww[k]));
+        acc[m] = fmaf(a.x, b.x, acc[m]);
+        acc[m] = fmaf(a.y, b.y, acc[m]);
+      }
+    }
+  }
+  for (uint32_t i = (D / 8u) * 8u + lane; i < D; i += 32u)        // tail when D % 8 != 0
+    for (uint32_t m = 0; m < nt; ++m)
+      acc[m] = fmaf(__half2float(x[(size_t)(t0 + m) * D + i]), __half2float(w[(size_t)e * D + i]), acc[m]);
+#pragma unroll
+  for (int m = 0; m < 8; ++m) {
+    const float v = warp_sum(acc[m]);
+    if (lane == 0 && (uint32_t)m < nt) y[(size_t)(t0 + m) * rows + e] = v;
+  }
+}
+cudaError_t launch_f16_matvec(const __half* x, const __half* w, float* y, uint32_t D, uint32_t rows, uint32_t tokens, cudaStream_t st) {
+  if (rows == 0 || tokens == 0) return cudaSuccess;
+  for (uint32_t t0 = 0; t0 < tokens; t0 += 8u * 65535u) {       // grid.y carries the token slab
+    const uint32_t nt = min(tokens - t0, 8u * 65535u);
+    dim3 grid((rows + 7) / 8, (nt + 7) / 8);
+    f16_matvec_kernel<<<grid, 256, 0, st>>>(x + (size_t)t0 * D, w, y + (size_t)t0 * rows, D, rows, nt);
+  }
   return cudaGetLastError();
 }
 

@@ -115,6 +115,9 @@ cudaError_t launch_unpack_codes_streamed(const uint32_t* W, uint8_t* codes, uint
 cudaError_t launch_dequant(const uint32_t* W, const __half* S, const __half* B, void* out, uint32_t N, uint32_t K,
                            int bits, uint32_t group_shift, bool affine, bool as_f16, cudaStream_t st);
 
+cudaError_t launch_embedding_affine(const int32_t* input_ids, const uint32_t* W, const __half* S, const __half* B, __half* out,
+                                    uint32_t seq_len, uint32_t D, uint32_t vocab, int bits, uint32_t* err, cudaStream_t st);
+cudaError_t launch_f16_matvec(const __half* x, const __half* w, float* y, uint32_t D, uint32_t rows, uint32_t tokens, cudaStream_t st);
 cudaError_t launch_route_topk(const float* logits, uint32_t* ids, float* scores, uint32_t tokens, uint32_t E,
                               uint32_t K, bool norm_topk, bool has_shared, cudaStream_t st);
 // seg_counts != nullptr: rows come in regions of seg_cap, only the first seg_counts[region] of each are computed

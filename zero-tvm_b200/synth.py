@@ -28,13 +28,15 @@ def pack_codes(q: np.ndarray, bits: int) -> np.ndarray:
         for i in range(8):
             out |= q[..., i::8].astype(np.uint32) << np.uint32(4 * i)
         return out
+    if bits == 8:
+        return np.ascontiguousarray(q).view("<u4").reshape(*lead, K // 4)
     if bits == 3:
         planes = np.empty((*lead, K, 3), dtype=np.uint8)
         for j in range(3):
             planes[..., j] = (q >> j) & 1
         by = np.packbits(planes.reshape(*lead, K * 3), axis=-1, bitorder="little")
         return np.ascontiguousarray(by).view("<u4").reshape(*lead, K * 3 // 32)
-    raise ValueError("bits must be 3 or 4")
+    raise ValueError("bits must be 3, 4 or 8")
 
 
 def make_weights(rng: np.random.Generator, N: int, K: int, *, bits: int = 4, group: int = 64,
