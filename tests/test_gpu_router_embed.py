@@ -48,7 +48,9 @@ def test_router_logits_block_shape(bits, T, backend, dev, oracle_c):
     assert np.isfinite(got).all()
     err = zo.rel_err_scaled(got, ref, 1e-3)
     record_parity(err, zo.rel_err(got, ref))
-    assert err <= 1e-4, err        # f32 output: far inside the path's 2e-3
+    assert err <= TOL, err
+    # logits feed a softmax: what matters is the absolute error against their spread (f32 accumulation, f32 output)
+    assert np.abs(got - ref).max() <= 1e-5 * np.sqrt(np.mean(ref * ref))
 
 
 @pytest.mark.parametrize("bits,entry", [(4, "embedding_affine"), (8, "embedding_affine_int8")])

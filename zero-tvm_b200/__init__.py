@@ -6,6 +6,7 @@ dequant-matmul family, behind a C ABI (include/ztvm_b200.h).
            groups, grids) on top of `capi`
 `synth`    seeded synthetic tensors in the kernels' layouts
 `build`    nvcc build of libztvm_b200.so
+`recorder` a decode step's dispatch sequence captured once into a CUDA graph
 `ingest`   MLX safetensors records -> the buffers the kernels bind (host side, numpy)
 
 There is no CPU implementation: importing is cheap, but creating a Context without the built
@@ -17,3 +18,4 @@ from . import backend  # noqa: F401
 from . import sharded  # noqa: F401,E402
 from . import build  # noqa: F401,E402
 from . import ingest  # noqa: F401,E402
+from . import recorder  # noqa: F401,E402

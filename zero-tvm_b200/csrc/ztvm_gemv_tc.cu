@@ -35,8 +35,12 @@ __host__ __device__ constexpr int tc_rounds(int nt) { return nt <= 4 ? 4 : 2; }
 // accumulator collects GPA = 8 / NT scale groups side by side (the B fragment of a column is zero in the MMAs of the
 // other groups), so the per-group fold after the MMAs is spread over the lanes of a quad instead of being repeated
 // by each of them: lane (g, c) owns columns 2c and 2c + 1.
-template <int NT, bool AFFINE>
-__global__ void __launch_bounds__(kTcWarps * 32, 1)
+// W = warps per CTA: 16 (one CTA per SM, the whole shared memory as its ring) for projections that keep an SM busy for
+// tens of microseconds; 8 (two CTAs fit an SM: registers and shared memory halve) for small ones, so that the CTAs of
+// the NEXT launch in the stream -- already started under programmatic dependent launch -- sit beside this launch's and
+// stream their first weights while it finishes, instead of waiting for the SM to empty.
+template <int NT, bool AFFINE, int W>
+__global__ void __launch_bounds__(W * 32, 16 / W)
 gemv_tc_kernel(const GemvParams p) {
   extern __shared__ __align__(128) uint8_t tc_smem[];
   constexpr int GPA = 8 / NT;                               // groups per accumulator (only 4 exist per tile)
@@ -47,8 +51,8 @@ gemv_tc_kernel(const GemvParams p) {
   const int g = lane >> 2, c = lane & 3;
 
   const uint32_t slices = p.K / kTcSlice;
-  const uint32_t KS = slices < (uint32_t)kTcWarps ? slices : (uint32_t)kTcWarps;
-  const uint32_t RG = (uint32_t)kTcWarps / KS;
+  const uint32_t KS = slices < (uint32_t)W ? slices : (uint32_t)W;
+  const uint32_t RG = (uint32_t)W / KS;
   const uint32_t ks = (uint32_t)warp % KS, rg = (uint32_t)warp / KS;
   const bool warp_active = rg < RG;
   const uint32_t num_kt = (slices + KS - 1) / KS;
@@ -62,8 +66,8 @@ gemv_tc_kernel(const GemvParams p) {
   const uint32_t total = num_kt * rounds;                   // (K tile, round) steps of every warp
 
   const uint32_t ring = (uint32_t)__cvta_generic_to_shared(tc_smem) + (uint32_t)warp * (kTcDepth * kTcTileBytes);
-  float* partial = reinterpret_cast<float*>(tc_smem + kTcRingBytes);            // [2][warps][kBlkRows][NT]
-  float* acc_sm = partial + 2 * kTcWarps * kBlkRows * NT;                       // [nrows][M], only if num_kt > 1
+  float* partial = reinterpret_cast<float*>(tc_smem + (W * kTcDepth * kTcTileBytes));            // [2][warps][kBlkRows][NT]
+  float* acc_sm = partial + 2 * W * kBlkRows * NT;                       // [nrows][M], only if num_kt > 1
 
   // ---- producer side: one (tile, slice) per step, issued kTcDepth - 1 steps ahead ----------------------------
   const uint32_t cp_row = (uint32_t)lane >> 3, cp_chunk = (uint32_t)lane & 7;   // codes: 4 rows x 8 chunks per pass
@@ -227,7 +231,7 @@ gemv_tc_kernel(const GemvParams p) {
         __syncwarp();   // every lane is done with the stage before the next issue refills it
       }
       // ---- meeting: K-slice partials of the block's rows -> shared, then one fixed-order sum per output --------
-      float* mine = partial + ((size_t)((meet & 1u) * kTcWarps + (uint32_t)warp) * kBlkRows) * NT;
+      float* mine = partial + ((size_t)((meet & 1u) * W + (uint32_t)warp) * kBlkRows) * NT;
 #pragma unroll
       for (int q = 0; q < kTcRounds; ++q)
 #pragma unroll
@@ -252,10 +256,10 @@ gemv_tc_kernel(const GemvParams p) {
           }
         }
       __syncthreads();
-      const float* buf = partial + (size_t)(meet & 1u) * kTcWarps * kBlkRows * NT;
+      const float* buf = partial + (size_t)(meet & 1u) * W * kBlkRows * NT;
       const uint32_t outs = (uint32_t)kTcRounds * RG * 16u * p.M;
       // the meeting's sums are taken by a different warp each time, so no warp falls behind the others for good
-      for (uint32_t i = (threadIdx.x + 512u - 32u * (meet & 15u)) & 511u; i < outs; i += blockDim.x) {
+      for (uint32_t i = (threadIdx.x + (uint32_t)(W * 32) - 32u * (meet & (uint32_t)(W - 1))) & (uint32_t)(W * 32 - 1); i < outs; i += blockDim.x) {
         const uint32_t tok = i % p.M, br = i / p.M;           // br: row inside the block's R*RG tiles
         const uint32_t r16 = br & 15u, tb = br >> 4;
         const uint32_t q = tb / RG, rgi = tb - q * RG;
@@ -284,6 +288,27 @@ gemv_tc_kernel(const GemvParams p) {
 }
 
 // ---- host side --------------------------------------------------------------------------------------------
+// Shared-memory accumulators (only when K spans several K tiles of W slices) must fit beside the ring.
+static bool tc_acc_fits(const GemvParams& p, int sm_count, int warps) {
+  const uint32_t slices = p.K / kTcSlice;
+  if (slices <= (uint32_t)warps) return true;
+  const uint32_t grid = p.N < (uint32_t)sm_count ? p.N : (uint32_t)sm_count;
+  const uint64_t rows = ((uint64_t)p.N + grid - 1) / grid + 1;
+  return rows * p.M * 4 <= (warps == 8 ? kTcMaxAccBytes / 2 : kTcMaxAccBytes);
+}
+// warps per CTA for a problem: 8 (two CTAs per SM) while an SM's share of the weights is small, else 16
+static int tc_warps_for(const GemvParams& p, int sm_count) {
+  static const int forced = [] { const char* e = getenv("ZTVM_GEMV_WARPS"); return e ? atoi(e) : 0; }();   // measurement knob
+  int w = 16;
+  if (forced == 8 || forced == 16) w = forced;
+  else if (p.K / kTcSlice <= 8u && (uint64_t)p.N * p.KP * 4 / (uint64_t)sm_count <= 384u * 1024u) w = 8;   // one K tile only
+  if (w == 8 && !tc_acc_fits(p, sm_count, 8)) w = 16;
+  return w;
+}
+static unsigned tc_grid_for(const GemvParams& p, int sm_count) {
+  return p.N < (uint32_t)sm_count ? p.N : (unsigned)sm_count;
+}
+
 bool gemv_tc_supported(const GemvParams& p, int bits, int sm_count) {
   if (bits != 4 || p.group_shift != 6 || p.M < 1 || p.M > 8) return false;
   if (p.K % kTcSlice || p.K == 0 || p.N == 0) return false;
@@ -291,29 +316,23 @@ bool gemv_tc_supported(const GemvParams& p, int bits, int sm_count) {
   if ((reinterpret_cast<uintptr_t>(p.W) & 15u) || (reinterpret_cast<uintptr_t>(p.S) & 7u) ||
       (p.B && (reinterpret_cast<uintptr_t>(p.B) & 7u)))
     return false;
-  const uint32_t slices = p.K / kTcSlice;
-  if (slices > (uint32_t)kTcWarps) {   // several K tiles: the running sums of the CTA's rows sit in shared memory
-    const uint32_t grid = p.N < (uint32_t)sm_count ? p.N : (uint32_t)sm_count;
-    const uint64_t rows = ((uint64_t)p.N + grid - 1) / grid + 1;
-    if (rows * p.M * 4 > kTcMaxAccBytes) return false;
-  }
-  return true;
+  return tc_acc_fits(p, sm_count, tc_warps_for(p, sm_count));
 }
 
-template <int NT, bool AFFINE>
+template <int NT, bool AFFINE, int W>
 static cudaError_t launch_tc_one(const GemvParams& p, unsigned grid, size_t smem, cudaStream_t st) {
-  auto kern = gemv_tc_kernel<NT, AFFINE>;
+  auto kern = gemv_tc_kernel<NT, AFFINE, W>;
   static bool attr_set[16] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 16 && !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, W == 16 ? 227 * 1024 : 112 * 1024);
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(kTcWarps * 32);
+  cfg.blockDim = dim3(W * 32);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
@@ -325,18 +344,23 @@ static cudaError_t launch_tc_one(const GemvParams& p, unsigned grid, size_t smem
   return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
-cudaError_t launch_gemv_tc(const GemvParams& p, int sm_count, cudaStream_t st) {
-  const unsigned grid = p.N < (uint32_t)sm_count ? p.N : (unsigned)sm_count;
+template <int W>
+static cudaError_t launch_tc_w(const GemvParams& p, int sm_count, cudaStream_t st) {
+  const unsigned grid = tc_grid_for(p, sm_count);
   const int nt = p.M == 1 ? 1 : p.M == 2 ? 2 : p.M <= 4 ? 4 : 8;
-  size_t smem = kTcRingBytes + (size_t)2 * kTcWarps * tc_rounds(nt) * 16 * nt * 4;
-  if (p.K / kTcSlice > (uint32_t)kTcWarps) smem += (((size_t)p.N + grid - 1) / grid + 1) * p.M * 4;
+  size_t smem = (size_t)W * kTcDepth * kTcTileBytes + (size_t)2 * W * tc_rounds(nt) * 16 * nt * 4;
+  if (p.K / kTcSlice > (uint32_t)W) smem += (((size_t)p.N + grid - 1) / grid + 1) * p.M * 4;
   const bool affine = p.B != nullptr;
   switch (nt) {
-    case 1: return affine ? launch_tc_one<1, true>(p, grid, smem, st) : launch_tc_one<1, false>(p, grid, smem, st);
-    case 2: return affine ? launch_tc_one<2, true>(p, grid, smem, st) : launch_tc_one<2, false>(p, grid, smem, st);
-    case 4: return affine ? launch_tc_one<4, true>(p, grid, smem, st) : launch_tc_one<4, false>(p, grid, smem, st);
-    default: return affine ? launch_tc_one<8, true>(p, grid, smem, st) : launch_tc_one<8, false>(p, grid, smem, st);
+    case 1: return affine ? launch_tc_one<1, true, W>(p, grid, smem, st) : launch_tc_one<1, false, W>(p, grid, smem, st);
+    case 2: return affine ? launch_tc_one<2, true, W>(p, grid, smem, st) : launch_tc_one<2, false, W>(p, grid, smem, st);
+    case 4: return affine ? launch_tc_one<4, true, W>(p, grid, smem, st) : launch_tc_one<4, false, W>(p, grid, smem, st);
+    default: return affine ? launch_tc_one<8, true, W>(p, grid, smem, st) : launch_tc_one<8, false, W>(p, grid, smem, st);
   }
+}
+
+cudaError_t launch_gemv_tc(const GemvParams& p, int sm_count, cudaStream_t st) {
+  return tc_warps_for(p, sm_count) == 8 ? launch_tc_w<8>(p, sm_count, st) : launch_tc_w<16>(p, sm_count, st);
 }
 
 }  // namespace ztvm
