@@ -369,12 +369,14 @@ def test_peer_store_expert_parallel_step_with_ranks_emulated_on_one_gpu(T, G, E,
         assert np.abs(got - ref).max() <= 5e-3 * np.abs(ref).max(), f"step {step}"
 
 
-def test_dispatch_plan_on_the_device_matches_the_tensor_op_plan(backend, dev):
+@pytest.mark.parametrize("T", [300, 640, 4200])
+def test_dispatch_plan_on_the_device_matches_the_tensor_op_plan(backend, dev, T):
     """ztvm_moe_dispatch_plan against the plan recomputed on the host: same pairs per destination, a
-    permutation of all pairs in destination order, the right local expert for every pair."""
+    permutation of all pairs in destination order, the right local expert for every pair. The sizes sit on both
+    sides of the pair counts where the planner changes kernels (one block up to 32768 pairs, several above)."""
     import torch
     from zero_tvm_b200 import sharded
-    T, K, E, world = 300, 8, 64, 4
+    K, E, world = 8, 64, 4
     epr = E // world
     rng = np.random.default_rng(17)
     ids_full = np.stack([rng.permutation(E)[:K + 1] for _ in range(T)]).astype(np.uint32)   # K routed + one more column

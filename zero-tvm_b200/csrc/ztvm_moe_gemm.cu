@@ -510,6 +510,7 @@ cudaError_t launch_moe_grouped(const GemvParams& g, uint32_t tokens, uint32_t sl
     attr_set[dev] = true;
   }
   const uint32_t max_tiles = (P + kMoeBM - 1) / kMoeBM + E;
+  if (max_tiles > 65535u) return cudaErrorInvalidConfiguration;   // grid.y; 65536 pairs and 1024 experts stay far below
   dim3 grid(g.N / kMoeBN, max_tiles);
   moe_gemm_w4_kernel<<<grid, kMoeThreads, smem, st>>>(tmap_w, p);
   return cudaGetLastError();
