@@ -56,6 +56,7 @@ struct MoeTaParams {
   const uint32_t* dst_index;
   uint32_t seg_cap;
   __half* y_seg[9];
+  uint32_t vec_out;                   // every output row starts on a 16-byte boundary: rows leave in 16-byte stores
 };
 
 struct MtaSmem {
@@ -65,8 +66,20 @@ struct MtaSmem {
   static constexpr int kOffW = kMtaXStages * kXBytes;
   static constexpr int kOffBar = kOffW + kMtaWStages * kWBytes;
   static constexpr int kOffUnits = kOffBar + 256;                // this CTA's first kMtaUnitTable units: expert, r0, rows, n0
-  static constexpr int kTotal = kOffUnits + kMtaUnitTable * 16;
+  static constexpr int kStagePitch = kMtaUnitRows * 2;           // epilogue stage: 32 pairs x 256 weight rows, f16
+  static constexpr int kOffStage = kOffUnits + kMtaUnitTable * 16;
+  static constexpr int kOffDst = kOffStage + 32 * kStagePitch;   // output row address of each pair of a unit, two units
+  static constexpr int kTotal = kOffDst + 2 * kMtaNP * 8;
 };
+
+// Named barrier 1: the epilogue warps among themselves (barrier 0 is __syncthreads).
+__device__ __forceinline__ void ep_bar() { asm volatile("bar.sync 1, %0;" ::"n"(kMtaEpWarps * 32) : "memory"); }
+__device__ __forceinline__ bool ep_bar_and(bool pred) {
+  uint32_t r;
+  asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbar.red.and.pred q, 1, %2, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+               : "=r"(r) : "r"((uint32_t)pred), "n"(kMtaEpWarps * 32) : "memory");
+  return r != 0u;
+}
 
 __global__ void __launch_bounds__(kMtaThreads, 1)
 moe_ta_kernel(const __grid_constant__ CUtensorMap tmap_w, const MoeTaParams p) {
@@ -371,20 +384,30 @@ moe_ta_kernel(const __grid_constant__ CUtensorMap tmap_w, const MoeTaParams p) {
     asm volatile("cp.async.wait_group 0;" ::: "memory");
   } else {
     // ================= epilogue: D[weight row][pair] in TMEM -> y rows of the pairs =================
+    // A thread holds one weight row of 32 pairs, an output row wants 256 weight rows of one pair side by side: the tile
+    // turns round in shared memory, 32 pairs at a time. Phase 1: every thread stores its 32 values as f16 into
+    // stage[pair][weight row] (a warp's 32 lanes fill 64 consecutive bytes). Phase 2: a warp reads one pair's 512 bytes
+    // (16 per lane) and stores them to the pair's output row in one instruction. The accumulators are free again as
+    // soon as the last 32 pairs have been read, before their rows have left.
     const int quarter = warp & 3;
     const uint32_t r_half = (uint32_t)(quarter * 32 + lane);
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-    bool ok = true;
-    for (uint32_t ui = 0; ui < my_units && ok; ++ui) {
+    const uint32_t stage = base + L::kOffStage;
+    unsigned long long* const dst_tabs = reinterpret_cast<unsigned long long*>(gen_base + L::kOffDst);
+    const uint4* const stage_g = reinterpret_cast<const uint4*>(gen_base + L::kOffStage);
+    const bool vec_out = p.vec_out != 0u;
+    for (uint32_t ui = 0; ui < my_units; ++ui) {
       uint32_t expert, r0, rows, n0;
       unit_of(ui, expert, r0, rows, n0);
-      if (!mbar_wait(bar_acc_full, ui & 1u, p.status, 5u, abort_flag)) { ok = false; break; }
-      tc_fence_after();
-      for (uint32_t cb = 0; cb * 32u < rows; ++cb) {
-        // lane i looks up where pair cb * 32 + i lives; the addresses are then passed round the warp
+      // where the output rows of this unit's pairs start: warp q looks up pairs 32 q .. 32 q + 31 while the unit's
+      // MMAs are still running (two dependent global loads per pair); two tables, so a slow warp may still be reading
+      // the previous unit's
+      unsigned long long* const dst_tab = dst_tabs + (ui & 1u) * (uint32_t)kMtaNP;
+      {
+        const uint32_t col = (uint32_t)quarter * 32u + (uint32_t)lane;
         unsigned long long my_dst = 0ull;
-        if (cb * 32u + lane < rows) {
-          const uint32_t pr = p.sc.sorted[r0 + cb * 32u + lane];
+        if (col < rows) {
+          const uint32_t pr = p.sc.sorted[r0 + col];
           if (p.dst_index) {
             my_dst = reinterpret_cast<unsigned long long>(p.y_seg[pr / p.seg_cap] + (size_t)p.dst_index[pr] * p.out_tok_stride);
           } else {
@@ -392,24 +415,59 @@ moe_ta_kernel(const __grid_constant__ CUtensorMap tmap_w, const MoeTaParams p) {
             my_dst = reinterpret_cast<unsigned long long>(p.Y + (size_t)tk * p.out_tok_stride + (size_t)sl * p.out_slot_stride);
           }
         }
-        const uint32_t lim = rows - cb * 32u;
+        dst_tab[col] = my_dst;
+      }
+      const bool got = mbar_wait(bar_acc_full, ui & 1u, p.status, 5u, abort_flag);
+      // the four warps leave together or not at all: none may be left alone at a barrier below
+      if (!ep_bar_and(got)) break;
+      tc_fence_after();
+      const bool two = n0 + kMtaRows < p.N;
+      const uint32_t ncb = (rows + 31u) / 32u;
+      for (uint32_t cb = 0; cb < ncb; ++cb) {
+        const uint32_t lim = min(32u, rows - cb * 32u);
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          const uint32_t n = n0 + (uint32_t)h * kMtaRows + r_half;
-          if (n0 + (uint32_t)h * kMtaRows >= p.N) break;           // warp-uniform
+          if (h == 1 && !two) break;                                   // warp-uniform
           uint32_t v[32];
           tmem_ld32(tmem_base + lane_base + (uint32_t)h * kMtaNP + cb * 32u, v);
           tmem_ld_wait();
+          const uint32_t col = stage + ((uint32_t)h * kMtaRows + r_half) * 2u;
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            const unsigned long long d = __shfl_sync(0xffffffffu, my_dst, i);
-            if ((uint32_t)i < lim && n < p.N) reinterpret_cast<__half*>(d)[n] = __float2half_rn(__uint_as_float(v[i]));
+            const unsigned short hv = __half_as_ushort(__float2half_rn(__uint_as_float(v[i])));
+            asm volatile("st.shared.u16 [%0], %1;" ::"r"(col + (uint32_t)i * (uint32_t)L::kStagePitch), "h"(hv) : "memory");
           }
         }
+        if (cb + 1 == ncb) {       // the accumulators have been read: the next unit's MMAs may start
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_acc_empty);
+        }
+        ep_bar();
+        // rows out: warp q takes pairs q, q + 4, ...; lane l the eight weight rows n0 + 8 l .. of the pair
+        const uint32_t n = n0 + 8u * (uint32_t)lane;
+        const bool mine = n < p.N && (two || lane < 16);               // N % 8 == 0: eight rows are in or out together
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t i = (uint32_t)quarter + 4u * (uint32_t)j;
+          if (i >= lim) break;
+          __half* const d = reinterpret_cast<__half*>(dst_tab[cb * 32u + i]) + n;
+          if (mine) {
+            const uint4 q = stage_g[i * (L::kStagePitch / 16) + lane];
+            if (vec_out) {
+              *reinterpret_cast<uint4*>(d) = q;
+            } else {
+              const uint32_t w4[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                d[2 * e] = __ushort_as_half((unsigned short)(w4[e] & 0xFFFFu));
+                d[2 * e + 1] = __ushort_as_half((unsigned short)(w4[e] >> 16));
+              }
+            }
+          }
+        }
+        ep_bar();                  // the stage is free for the next 32 pairs
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_acc_empty);
     }
   }
   tc_fence_before();
@@ -482,6 +540,10 @@ cudaError_t launch_moe_ta(const GemvParams& g, uint32_t tokens, uint32_t slots, 
   p.sc = sc; p.status = status;
   p.dst_index = g.dst_index; p.seg_cap = g.seg_cap ? g.seg_cap : 1u;
   for (int i = 0; i < 9; ++i) p.y_seg[i] = reinterpret_cast<__half*>(g.y_seg[i]);
+  uintptr_t lowbits = ((uintptr_t)g.out_tok_stride | (uintptr_t)g.out_slot_stride) * 2u;
+  if (g.dst_index) { for (int i = 0; i < 9; ++i) lowbits |= reinterpret_cast<uintptr_t>(g.y_seg[i]); }
+  else lowbits |= reinterpret_cast<uintptr_t>(g.Y);
+  p.vec_out = (lowbits & 15u) == 0 ? 1u : 0u;
   constexpr int smem = MtaSmem::kTotal + 1024;
   static bool attr_set[64] = {};
   static std::mutex mu;
