@@ -104,6 +104,31 @@ def _worker(rank, world, port, q):
         tl = T // world
         y = moe.forward(_t(mb["x"][rank * tl:(rank + 1) * tl]), _t(mb["logits"][rank * tl:(rank + 1) * tl]))
         q.put(("moe", 0, rank, y.numpy().copy()))
+        if world > 1:
+            # ---- one expert id out of range, through a device-style plan hook -------------------------
+            # The C ABI counts such an id and leaves its pair out of the plan; the hook below does the same and, like
+            # the device kernel, fills only the first sum(send_counts) entries of order / local_expert.
+            class DroppingKernels(OracleKernels):
+                def route_topk(self, ids, scores, logits, E, K, tokens):
+                    super().route_topk(ids, scores, logits, E, K, tokens)
+                    if rank == 0:
+                        ids[1, 0] = 1000
+
+                def dispatch_plan(self, ids_routed, epr, world_):
+                    flat = ids_routed.reshape(-1).to(torch.int64)
+                    good = torch.nonzero(flat < epr * world_).reshape(-1)
+                    dest = torch.div(flat[good], epr, rounding_mode="floor")
+                    o = good[torch.argsort(dest, stable=True)]
+                    order = torch.full((flat.numel(),), 2**31 - 1, dtype=torch.int64)      # garbage past the prefix
+                    local = torch.full((flat.numel(),), -7, dtype=torch.int32)
+                    order[:o.numel()] = o
+                    local[:o.numel()] = (flat[o] % epr).to(torch.int32)
+                    return order, local, torch.bincount(dest, minlength=world_)[:world_]
+
+            bad = sharded.ExpertParallelMoE(DroppingKernels(), stacks["gate"], stacks["up"], stacks["down"], E=E, top_k=top_k,
+                                            d=d, ffn=ffn)
+            yb = bad.forward(_t(mb["x"][rank * tl:(rank + 1) * tl]), _t(mb["logits"][rank * tl:(rank + 1) * tl]))
+            q.put(("moe_bad", 0, rank, yb.numpy().copy()))
     finally:
         dist.destroy_process_group()
 
@@ -117,7 +142,7 @@ def _run(world):
         p.start()
     import queue as _queue
     out = []
-    while len(out) < 3 * world:
+    while len(out) < (3 if world == 1 else 4) * world:
         try:
             out.append(q.get(timeout=2))
         except _queue.Empty:
@@ -158,3 +183,8 @@ def test_two_ranks_equal_one_rank():
     mb = z.synth.moe_block(12, E=8, hidden=256, ffn=128, seed=5)
     ref = zo.moe_block(mb["x"], mb["logits"], mb["gate"], mb["up"], mb["down"], 8, 2, 128)["y"].astype(np.float64)
     assert np.abs(one[("moe", 0)].astype(np.float64) - ref).max() <= 5e-3 * np.abs(ref).max()
+    # a pair with an out-of-range expert id is left out (contributes nothing); every other token is untouched
+    ybad = np.concatenate([y for k, m, r, y in sorted((t for t in two if t[0] == "moe_bad"), key=lambda t: t[2])])
+    assert np.isfinite(ybad.astype(np.float64)).all()
+    same = (ybad.view(np.uint16) == ymoe.view(np.uint16)).all(axis=1)
+    assert same.sum() == ymoe.shape[0] - 1 and not same[1]

@@ -164,7 +164,7 @@ moe_ta_kernel(const __grid_constant__ CUtensorMap tmap_w, const MoeTaParams p) {
         unit_of(ui, expert, r0, rows, n0);
         for (uint32_t c = 0; c < num_chunks; ++c, ++gc) {
           const uint32_t s = gc % kMtaWStages, ph = (gc / kMtaWStages) & 1u;
-          if (gc >= (uint32_t)kMtaWStages && !mbar_wait(bar_w_empty(s), ph ^ 1u, p.status, 6u, abort_flag)) { ok = false; break; }
+          if (gc >= (uint32_t)kMtaWStages && !mbar_wait(bar_w_empty(s), ph ^ 1u, p.status, 6u, abort_flag, 400u)) { ok = false; break; }
           mbar_arrive_expect_tx(bar_w_full(s), (uint32_t)L::kWBytes);
           tma_load_2d(w_ring + s * L::kWBytes, &tmap_w, bar_w_full(s), (int)(c * 32), (int)(expert * p.N + n0));
           tma_load_2d(w_ring + s * L::kWBytes + L::kWHalf, &tmap_w, bar_w_full(s), (int)(c * 32), (int)(expert * p.N + n0 + kMtaRows));
@@ -417,7 +417,7 @@ moe_ta_kernel(const __grid_constant__ CUtensorMap tmap_w, const MoeTaParams p) {
         }
         dst_tab[col] = my_dst;
       }
-      const bool got = mbar_wait(bar_acc_full, ui & 1u, p.status, 5u, abort_flag);
+      const bool got = mbar_wait(bar_acc_full, ui & 1u, p.status, 5u, abort_flag, 400u);
       // the four warps leave together or not at all: none may be left alone at a barrier below
       if (!ep_bar_and(got)) break;
       tc_fence_after();

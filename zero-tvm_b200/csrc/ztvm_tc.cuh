@@ -34,8 +34,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait: false (and a raised status word) when the phase does not complete in about a second.
+// `nap_ns`: sleep between polls. A role that waits for a whole main loop (an epilogue, a producer many slots ahead)
+// passes a long nap: its polls are instructions taken from the warps that have work.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t* status, uint32_t code,
-                                          volatile uint32_t* abort_flag) {
+                                          volatile uint32_t* abort_flag, uint32_t nap_ns = 40u) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (true) {
@@ -44,7 +46,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_
 #pragma unroll 1
     for (int i = 0; i < 32; ++i) {
       if (mbar_try_wait(bar, parity)) return true;
-      __nanosleep(40);
+      __nanosleep(nap_ns);
     }
     if (*abort_flag) return false;
     if ((unsigned long long)(clock64() - t0) > kWaitCycles) {
