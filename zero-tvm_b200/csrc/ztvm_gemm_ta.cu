@@ -15,15 +15,16 @@
 // 32 (w % 4) .. +31, so it owns those 32 weight rows, and the two warps that share a lane quarter split the k block
 // in halves (16 TMEM columns each); warp 1 allocates tensor memory and issues the MMAs. Every wait is bounded
 // (status word, as in ztvm_gemm.cu).
+#include <type_traits>
 #include "ztvm_kernels.h"
 #include "ztvm_tc.cuh"
 
 namespace ztvm {
 
 constexpr int kTaStages = 4;        // activation tiles in shared memory and weight slices in tensor memory
-constexpr int kTaWStages = 2;       // packed-weight ring (each slot holds four k blocks)
+constexpr int kTaWStages = 3;       // packed-weight ring (each slot holds four k blocks)
 constexpr int kTaWChunk = 4;
-constexpr int kTaDqWarps = 8;
+constexpr int kTaDqWarps = 16;      // two teams of eight: a team takes every other k block
 constexpr int kTaThreads = 96 + kTaDqWarps * 32;
 constexpr int kTaRows = 128;        // weight rows per CTA = TMEM lanes
 
@@ -74,7 +75,7 @@ gemm_w4_ta_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
   // barrier: they fly while tensor memory is allocated.
   if (threadIdx.x == 0) {
     for (int s = 0; s < kTaStages; ++s) {
-      mbar_init(bar_full(s), 1 + kTaDqWarps * 32);   // the activation tile (with its byte count) + every dequantiser thread
+      mbar_init(bar_full(s), 1 + (kTaDqWarps / 2) * 32);   // the activation tile (with its byte count) + every thread of the team that writes the slice
       mbar_init(bar_empty(s), 1);
     }
     mbar_init(bar_accum, 1);
@@ -105,6 +106,23 @@ gemm_w4_ta_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), kTmemCols);
     tmem_relinquish();
+  }
+  // The dequantisers' first scales and biases (16 groups of this thread's row) are requested before the block barrier:
+  // weights are not written by the previous kernel in the stream, and the DRAM latency of these loads would otherwise
+  // sit between the barrier and the first dequantised stage.
+  uint4 sv_pre0 = make_uint4(0, 0, 0, 0), bv_pre0 = sv_pre0, sv_pre1 = sv_pre0, bv_pre1 = sv_pre0;
+  const bool vec_sb_all = p.group_shift == 6 && (p.SPR % 8u) == 0 &&
+                          ((reinterpret_cast<uintptr_t>(p.S) | reinterpret_cast<uintptr_t>(p.B)) & 15u) == 0;
+  if (warp >= 3 && vec_sb_all) {
+    const uint32_t row_pre = min(n0 + (uint32_t)((warp & 3) * 32 + lane), p.N - 1);
+    const unsigned short* sp = reinterpret_cast<const unsigned short*>(p.S) + (size_t)row_pre * p.SPR;
+    const unsigned short* bp = reinterpret_cast<const unsigned short*>(p.B) + (size_t)row_pre * p.SPR;
+    sv_pre0 = __ldg(reinterpret_cast<const uint4*>(sp));
+    if (AFFINE) bv_pre0 = __ldg(reinterpret_cast<const uint4*>(bp));
+    if (num_kb > 8u) {
+      sv_pre1 = __ldg(reinterpret_cast<const uint4*>(sp + 8));
+      if (AFFINE) bv_pre1 = __ldg(reinterpret_cast<const uint4*>(bp + 8));
+    }
   }
   tc_fence_before();
   __syncthreads();
@@ -141,18 +159,25 @@ gemm_w4_ta_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
       constexpr uint32_t idesc = idesc_f16(NT);
       const uint64_t b0 = smem_desc_sw128(x_ring);
       uint32_t s = 0, ph = 0;
-      bool ok = true;
-      for (uint32_t kb = 0; kb < num_kb; ++kb) {
-        ok = mbar_wait(bar_full(s), ph, p.status, 2u, abort_flag);
-        if (!ok) break;
+      // The thread is held at each tcgen05.mma until the pipe takes it, so a barrier poll between two k blocks would
+      // be a bubble in the pipe: the next block's barrier is polled once before the last MMA of the current block is
+      // issued, in the shadow of the MMAs already queued, and waited for afterwards only if that poll failed.
+      bool ok = mbar_wait(bar_full(0), 0u, p.status, 2u, abort_flag);
+      for (uint32_t kb = 0; kb < num_kb && ok; ++kb) {
         tc_fence_after();
         const uint64_t bdesc = b0 + (uint64_t)(s * (L::kXBytes >> 4));
         const uint32_t a_tmem = tmem_base + kColA + s * 32u;
+        uint32_t s1 = s + 1u, ph1 = ph;
+        if (s1 == (uint32_t)kTaStages) { s1 = 0; ph1 ^= 1u; }
+        bool next_ready = true;
 #pragma unroll
-        for (int k = 0; k < kGemmBK / 16; ++k)   // 16 k elements: 8 TMEM columns of A, 32 bytes along the swizzled B row
+        for (int k = 0; k < kGemmBK / 16; ++k) {   // 16 k elements: 8 TMEM columns of A, 32 bytes along the swizzled B row
+          if (k == kGemmBK / 16 - 1 && kb + 1 < num_kb) next_ready = mbar_try_wait(bar_full((int)s1), ph1);
           umma_f16_ta(tmem_base, a_tmem + (uint32_t)(8 * k), bdesc + (uint64_t)(2 * k), idesc, (kb | (uint32_t)k) ? 1u : 0u);
-        umma_commit(bar_empty(s));   // the activation tile and the weight slice are free once these MMAs have read them
-        if (++s == (uint32_t)kTaStages) { s = 0; ph ^= 1u; }
+        }
+        umma_commit(bar_empty((int)s));   // the activation tile and the weight slice are free once these MMAs have read them
+        if (!next_ready) ok = mbar_wait(bar_full((int)s1), ph1, p.status, 2u, abort_flag);
+        s = s1; ph = ph1;
       }
       if (ok) umma_commit(bar_accum);
     }
@@ -179,9 +204,16 @@ gemm_w4_ta_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
       }
     }
   } else {
-    // ================= dequantisers (warps 3..10), then epilogue =================
+    // ================= dequantisers (warps 3..18), then epilogue =================
+    // Two teams of eight warps take the k blocks in turn (team = k block mod 2). Inside a team, thread
+    // (quarter, lane) of half h owns weight row 32 quarter + lane and the 32-code half h of the block. A warp runs its
+    // block as one dependent chain (wait, load, dequantise, store to tensor memory, wait for the store, arrive), about
+    // twice as long as the tensor pipe needs for the block's MMAs: with one team the pipe idles half of the time, with
+    // two the chains of consecutive blocks overlap.
     const int quarter = warp & 3;                       // TMEM lanes this warp may touch: [32 * quarter, +32)
-    const uint32_t part = (uint32_t)(warp - 3) >> 2;    // which half of the k block (the two warps of a quarter)
+    const uint32_t wpart = (uint32_t)(warp - 3) >> 2;   // 0..3
+    const uint32_t part = wpart & 1u;                   // which half of the k block
+    const uint32_t team = wpart >> 1;
     const uint32_t r_tile = (uint32_t)(quarter * 32 + lane);
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     const int gshift = (int)p.group_shift;
@@ -190,8 +222,8 @@ gemm_w4_ta_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
     const unsigned short* brow = reinterpret_cast<const unsigned short*>(p.B) + (size_t)row * p.SPR;
     bool ok = true;
     // group 64: eight groups per 16-byte load, fetched eight k blocks ahead; scalar loads otherwise
-    const bool vec_sb = gshift == 6 && (p.SPR % 8u) == 0 && ((reinterpret_cast<uintptr_t>(p.S) | reinterpret_cast<uintptr_t>(p.B)) & 15u) == 0;
-    uint4 sv_cur = make_uint4(0, 0, 0, 0), bv_cur = sv_cur, sv_nxt = sv_cur, bv_nxt = sv_cur;
+    const bool vec_sb = vec_sb_all;
+    uint4 sv_cur = sv_pre0, bv_cur = bv_pre0, sv_nxt = sv_pre1, bv_nxt = bv_pre1;
     auto load_sb8 = [&](uint4& sv, uint4& bv, uint32_t kb8) {
       if (kb8 >= num_kb) return;
       sv = __ldg(reinterpret_cast<const uint4*>(srow + kb8));
@@ -201,72 +233,119 @@ gemm_w4_ta_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
       const uint32_t wsel = (i >> 1) == 0 ? v.x : (i >> 1) == 1 ? v.y : (i >> 1) == 2 ? v.z : v.w;
       return (unsigned short)((i & 1) ? (wsel >> 16) : (wsel & 0xFFFFu));
     };
-    if (vec_sb) { load_sb8(sv_cur, bv_cur, 0); load_sb8(sv_nxt, bv_nxt, 8); }
 
     const uint8_t* const wrow_sm = gen_base + L::kOffW + (r_tile >> 3) * 1024 + (r_tile & 7) * 128;
     constexpr int kUnroll = 8;
-    for (uint32_t kb0 = 0; kb0 < num_kb && ok; kb0 += kUnroll) {
+    auto run = [&](auto team_c) {
+      constexpr int TEAM = decltype(team_c)::value;
+      for (uint32_t kb0 = 0; kb0 < num_kb && ok; kb0 += kUnroll) {
 #pragma unroll
-      for (int i = 0; i < kUnroll; ++i) {
-        const uint32_t kb = kb0 + i;
-        if (kb >= num_kb || !ok) break;
-        const int s = (int)(kb % kTaStages);
-        const uint32_t ph = (kb / kTaStages) & 1u;
-        const uint32_t c = kb / kTaWChunk;
+        for (int i = TEAM; i < kUnroll; i += 2) {
+          const uint32_t kb = kb0 + i;
+          if (kb >= num_kb || !ok) break;
+          const int s = (int)(kb % kTaStages);
+          const uint32_t ph = (kb / kTaStages) & 1u;
+          const uint32_t c = kb / kTaWChunk;
+          const int ws = (int)(c % kTaWStages);
+          const int j = i % kTaWChunk;
+          if (j == TEAM) ok = mbar_wait(bar_w_full(ws), (c / kTaWStages) & 1u, p.status, 7u, abort_flag);
+          uint4 wv = make_uint4(0, 0, 0, 0);
+          if (ok) wv = *reinterpret_cast<const uint4*>(wrow_sm + ws * L::kWBytes + ((((uint32_t)j * 2 + part) ^ (r_tile & 7)) << 4));
+          // the TMEM slice of stage s was last read by the MMAs of k block kb - kTaStages
+          if (ok && kb >= (uint32_t)kTaStages) {
+            ok = mbar_wait(bar_empty(s), ph ^ 1u, p.status, 4u, abort_flag);
+            tc_fence_after();
+          }
+          if (ok) {
+            unsigned short s16, b16 = 0;
+            if (vec_sb) {
+              s16 = pick16(sv_cur, i);
+              if (AFFINE) b16 = pick16(bv_cur, i);
+            } else {
+              const uint32_t g = (kb * kGemmBK + part * 32) >> gshift;
+              s16 = __ldg(srow + g);
+              if (AFFINE) b16 = __ldg(brow + g);
+            }
+            const DqGroup dq = dq_group<AFFINE>(s16, b16);
+            const uint32_t words[4] = {wv.x, wv.y, wv.z, wv.w};
+            uint32_t a[16];
+#pragma unroll
+            for (int wi = 0; wi < 4; ++wi) {
+              const uint4 v = dequant_word_w16<AFFINE>(words[wi], dq);
+              a[4 * wi] = v.x; a[4 * wi + 1] = v.y; a[4 * wi + 2] = v.z; a[4 * wi + 3] = v.w;
+            }
+            // 32 weights of this row = 16 TMEM columns (two k-adjacent f16 per column) of this thread's lane
+            tmem_st16(tmem_base + lane_base + kColA + (uint32_t)s * 32u + part * 16u, a);
+            tmem_st_wait();
+          }
+          // the packed slot goes back to the producer only after the stores that consumed its words; a warp signals
+          // after its team's last k block of the slot
+          if (j + 2 >= kTaWChunk || kb + 2 >= num_kb) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_w_empty(ws));
+          }
+          tc_fence_before();
+          mbar_arrive(bar_full(s));   // every thread arrives itself (also on abort)
+        }
+        if (vec_sb) {
+          sv_cur = sv_nxt; bv_cur = bv_nxt;
+          load_sb8(sv_nxt, bv_nxt, kb0 + 2 * kUnroll);
+        }
+      }
+      // a last slot that holds one k block only has nothing for the second team: it still hands the slot back
+      if (TEAM == 1 && (num_kb % kTaWChunk) == 1u) {
+        const uint32_t c = (num_kb - 1u) / kTaWChunk;
         const int ws = (int)(c % kTaWStages);
-        const int j = i % kTaWChunk;
-        if (j == 0) ok = mbar_wait(bar_w_full(ws), (c / kTaWStages) & 1u, p.status, 7u, abort_flag);
-        uint4 wv = make_uint4(0, 0, 0, 0);
-        if (ok) wv = *reinterpret_cast<const uint4*>(wrow_sm + ws * L::kWBytes + ((((uint32_t)j * 2 + part) ^ (r_tile & 7)) << 4));
-        // the TMEM slice of stage s was last read by the MMAs of k block kb - kTaStages
-        if (ok && kb >= (uint32_t)kTaStages) {
-          ok = mbar_wait(bar_empty(s), ph ^ 1u, p.status, 4u, abort_flag);
-          tc_fence_after();
-        }
-        if (ok) {
-          unsigned short s16, b16 = 0;
-          if (vec_sb) {
-            s16 = pick16(sv_cur, i);
-            if (AFFINE) b16 = pick16(bv_cur, i);
-          } else {
-            const uint32_t g = (kb * kGemmBK + part * 32) >> gshift;
-            s16 = __ldg(srow + g);
-            if (AFFINE) b16 = __ldg(brow + g);
-          }
-          const DqGroup dq = dq_group<AFFINE>(s16, b16);
-          const uint32_t words[4] = {wv.x, wv.y, wv.z, wv.w};
-          uint32_t a[16];
-#pragma unroll
-          for (int wi = 0; wi < 4; ++wi) {
-            const uint4 v = dequant_word_w16<AFFINE>(words[wi], dq);
-            a[4 * wi] = v.x; a[4 * wi + 1] = v.y; a[4 * wi + 2] = v.z; a[4 * wi + 3] = v.w;
-          }
-          // 32 weights of this row = 16 TMEM columns (two k-adjacent f16 per column) of this thread's lane
-          tmem_st16(tmem_base + lane_base + kColA + (uint32_t)s * 32u + part * 16u, a);
-          tmem_st_wait();
-        }
-        // the packed slot goes back to the producer only after the stores that consumed its words
-        if (j == kTaWChunk - 1 || kb + 1 == num_kb) {
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar_w_empty(ws));
-        }
-        tc_fence_before();
-        mbar_arrive(bar_full(s));   // every thread arrives itself (also on abort)
+        if (ok) ok = mbar_wait(bar_w_full(ws), (c / kTaWStages) & 1u, p.status, 7u, abort_flag);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_w_empty(ws));
       }
-      if (vec_sb) {
-        sv_cur = sv_nxt; bv_cur = bv_nxt;
-        load_sb8(sv_nxt, bv_nxt, kb0 + 2 * kUnroll);
-      }
-    }
+    };
+    if (team == 0) run(std::integral_constant<int, 0>{}); else run(std::integral_constant<int, 1>{});
     // ---- epilogue: D[weight row][token] in TMEM -> y[token][weight row] ------------------------------------------
     const bool acc_ok = ok && mbar_wait(bar_accum, 0u, p.status, 5u, abort_flag);
     tc_fence_after();
     asm volatile("griddepcontrol.wait;" ::: "memory");   // y may still be read by the previous kernel in the stream
-    if (acc_ok) {
-      const uint32_t n = n0 + r_tile;
-      const int half = (int)part;                        // the two warps of a quarter take alternate token blocks
+    // f16 rows of whole 16-byte pieces: the tile is turned round in the (now idle) activation ring. Phase 1: a thread
+    // stores its weight row's 32 tokens of a block as f16 into stage[token][row] (a warp fills 64 consecutive bytes
+    // per instruction). Phase 2: half a warp reads one token's 256 bytes and stores them to y in 16-byte pieces.
+    // All sixteen warps reach the named barrier (also when a wait ran out: they then skip the memory work).
+    static_assert(NT * kTaRows * 2 <= kTaStages * L::kXBytes, "the output stage lives in the activation ring");
+    const bool staged = !p.out_f32 && (p.N % 8u) == 0;
+    if (staged) {
+      const uint32_t stage = x_ring;
+      if (acc_ok) {
 #pragma unroll 1
-      for (int cb = half; cb < NT / 32; cb += 2) {
+        for (int cb = (int)wpart; cb < NT / 32; cb += 4) {
+          uint32_t v[32];
+          tmem_ld32(tmem_base + lane_base + (uint32_t)(cb * 32), v);
+          tmem_ld_wait();
+          const uint32_t col = stage + (uint32_t)(cb * 32) * (kTaRows * 2u) + r_tile * 2u;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const unsigned short hv = __half_as_ushort(__float2half_rn(__uint_as_float(v[i])));
+            asm volatile("st.shared.u16 [%0], %1;" ::"r"(col + (uint32_t)i * (kTaRows * 2u)), "h"(hv) : "memory");
+          }
+        }
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(kTaDqWarps * 32) : "memory");
+      if (acc_ok) {
+        const uint32_t w16 = (uint32_t)(warp - 3);                 // 0..15
+        const uint32_t sub = (uint32_t)lane >> 4, piece = (uint32_t)lane & 15u;
+        const uint32_t n = n0 + piece * 8u;
+        const uint4* const stage_g = reinterpret_cast<const uint4*>(gen_base);
+#pragma unroll 4
+        for (uint32_t t = w16 * 2u + sub; t < (uint32_t)NT; t += 2u * kTaDqWarps) {
+          const uint32_t m = m0 + t;
+          if (m < p.M && n < p.N)
+            *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(p.Y) + (size_t)m * p.N + n) = stage_g[t * (kTaRows * 2u / 16u) + piece];
+        }
+      }
+    } else if (acc_ok) {
+      const uint32_t n = n0 + r_tile;
+      // the four warps of a quarter take the 32-token blocks in turn
+#pragma unroll 1
+      for (int cb = (int)wpart; cb < NT / 32; cb += 4) {
         uint32_t v[32];
         tmem_ld32(tmem_base + lane_base + (uint32_t)(cb * 32), v);
         tmem_ld_wait();
