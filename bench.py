@@ -516,6 +516,76 @@ def quick_device_rate(ctx, torch, device, z, workload, steps, warmup, seed=4321)
             "verified": {"max_rel_err": err, "max_rel_err_pure": zo.rel_err(got, y64), "ok": bool(err <= 2e-3 and np.abs(got).max() > 0)}}
 
 
+def fused_ffn_rate(ctx, torch, device, z, steps, warmup, ffn=12288, K=4096, seed=777):
+    """FFN front half of the dense decode layer (gate and up over hidden 4096 -> 12288, SiLU * up) as ONE call of
+    ztvm_fused_ffn against the engine's affine path (the [2 ffn, K] matmul, then silu_mul): same method as the other
+    decode rates (rotating weight sets >= 4x L2, graph replay, events on the launching stream), verified against the oracle."""
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    N = 2 * ffn
+    per_set = algorithmic_bytes(N, K, 1)
+    R = max(2, int(np.ceil(4 * L2_BYTES / per_set)))
+    sets = []
+    for _ in range(R):
+        W = torch.randint(-2**31, 2**31 - 1, (N, K // 8), dtype=torch.int32, device=device, generator=g)
+        s = (torch.randn((N, K // 64), device=device, generator=g) * 0.01).abs().to(torch.float16)
+        b = (torch.randn((N, K // 64), device=device, generator=g) * 0.05).to(torch.float16)
+        sets.append((W, s, b))
+    x = torch.randn((1, K), device=device).to(torch.float16)
+    h = torch.empty((1, ffn), dtype=torch.float16, device=device)
+    gu = torch.empty((1, N), dtype=torch.float16, device=device)
+    stream = torch.cuda.Stream(device)
+    d_f, d_u = z.MmDesc(K, ffn, 1, 64, 4, 1, 0), z.MmDesc(K, N, 1, 64, 4, 1, 0)
+
+    def fused():
+        for W, s, b in sets:
+            ctx.fused_ffn(d_f, h, x, s, W, b, stream)
+
+    def unfused():
+        for W, s, b in sets:
+            ctx.int4_matmul(d_u, gu, x, s, W, b, stream)
+            ctx.silu_mul(1, ffn, h, gu, stream)
+
+    out = {}
+    with torch.cuda.stream(stream):
+        for name, fn in (("fused", fused), ("unfused", unfused)):
+            fn()
+            stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                fn()
+            for _ in range(warmup):
+                graph.replay()
+            stream.synchronize()
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record(stream)
+            for _ in range(steps):
+                graph.replay()
+            ev1.record(stream)
+            stream.synchronize()
+            out[name] = ev0.elapsed_time(ev1) * 1e3 / (steps * R)      # us per FFN front half
+            del graph
+    from oracle import ztvm_oracle as zo
+    W, s, b = sets[-1]
+    with torch.cuda.stream(stream):
+        ctx.fused_ffn(d_f, h, x, s, W, b, stream)
+        stream.synchronize()
+    rows = slice(0, 256)          # the anchor over a slice of the outputs (gate rows 0..255 and their up rows)
+    Wn, sn, bn = (t.cpu().numpy() for t in (W, s, b))
+    sel = np.r_[0:256, ffn:ffn + 256]
+    ref = zo.fused_ffn_f64(x.cpu().numpy(), Wn[sel].view(np.uint32), sn[sel], bn[sel], 256)
+    got = h[:, rows].float().cpu().numpy()
+    err = zo.rel_err_scaled(got, ref, 1e-3)
+    peak = measured_peaks()["hbm"]
+    nbytes = per_set - N * 2 + ffn * 2          # the fused call writes ffn outputs, not 2 ffn
+    del sets
+    torch.cuda.empty_cache()
+    return {"workload": "ffn_gate_up_silu_m1", "value": nbytes / (out["fused"] * 1e-6) / 1e9, "unit": "GB/s",
+            "frac": nbytes / (out["fused"] * 1e-6) / 1e9 / peak, "peak": peak, "avg_launch_us": out["fused"], "launches": int(steps * R),
+            "unfused_us": out["unfused"], "unfused_launches_per_call": 2, "traffic": None,
+            "verified": {"max_rel_err": err, "max_rel_err_pure": zo.rel_err(got, ref), "ok": bool(err <= 2e-3 and np.abs(got).max() > 0)}}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -693,6 +763,7 @@ def main():
             decode = [quick_device_rate(ctx, torch, device, z, w, max(3, args.steps // 2), args.warmup)
                       for w in ("decode_gemv", "decode_layer_set", "decode_layer_set_fused", "shape:151936x4096x1xf32",
                                 "shape:12288x4096x1xq3")]
+            decode.append(fused_ffn_rate(ctx, torch, device, z, max(3, args.steps // 2), args.warmup))
             workload_shapes(args.workload)      # back to the main workload's code width
         if world > 1:
             dist.barrier()

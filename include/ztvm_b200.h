@@ -256,6 +256,18 @@ ZTVM_API ztvm_status ztvm_int4_matmul_moe_ep(ztvm_ctx* ctx, const ztvm_moe_desc*
 ZTVM_API ztvm_status ztvm_silu_mul_rows(ztvm_ctx* ctx, const ztvm_moe_ep_rows* rows, uint32_t ffn, void* h, const void* gate_up,
                                void* stream);
 
+/* Fused FFN front half: h[m][i] = f16(up_i * gate_i / (1 + exp(-gate_i))) with gate_i = x[m] . W[i], up_i = x[m] . W[ffn + i],
+ * both dot products and the activation in f32, one rounding at the store. `desc->N` is ffn (the output width); the
+ * weight, scales and biases hold 2 * ffn rows, gate rows first. Replaces fused_ffn (src/compiler/shaders/fused_ffn.wgsl:
+ * bindings [output, input, scales, weights, PODArgs]; symmetric group 32 there) and is the affine sibling the engine
+ * lacks (src/zero-tvm/engine-core.ts:2513-2519 pays gate_up matmul + silu_mul on affine models).
+ * 4-bit, group 64, K % 256 == 0, M <= 8: ONE launch of the persistent GEMV, whose CTAs own gate and up tiles of the
+ * same output rows. Other shapes (group 32 / 128, 3-bit, 8-bit, M > 8): the 2 * ffn-row matmul into an f32 buffer of
+ * the context (grown on demand: device synchronise + cudaMalloc when a call needs more than any before it), then the
+ * activation -- same arithmetic, two launches. desc->out_f32 must be 0. */
+ZTVM_API ztvm_status ztvm_fused_ffn(ztvm_ctx* ctx, const ztvm_mm_desc* desc, void* h, const void* x, const void* scales,
+                           const void* packed_w, const void* biases, void* stream);
+
 /* h[r][i] = f16(up * gate * 1/(1+exp(-gate))) over rows of [gate(ffn) | up(ffn)] f16.
  * Replaces silu_mul (src/compiler/shaders/silu_mul.wgsl:26-44). */
 ZTVM_API ztvm_status ztvm_silu_mul(ztvm_ctx* ctx, uint32_t rows, uint32_t ffn, void* h, const void* gate_up, void* stream);

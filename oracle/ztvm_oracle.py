@@ -481,3 +481,24 @@ def reference_router_expected(case) -> np.ndarray:
     xg = x.reshape(D // 64, 64)
     dot = (q.reshape(rows, D // 64, 64) * xg[None]).sum(axis=2)
     return (case["scales"].astype(F64) * dot + case["biases"].astype(F64) * xg.sum(axis=1)[None]).sum(axis=1)
+
+
+def fused_ffn_f64(x, W, scales, biases, ffn: int, group: int = 64, bits: int = 4, affine: bool = True) -> np.ndarray:
+    """fp64 anchor of the fused FFN front half (src/compiler/shaders/fused_ffn.wgsl:63-131): gate = x . W[i],
+    up = x . W[ffn + i] over the f32 dequantised weights, h = up * gate / (1 + exp(-gate)); nothing is rounded."""
+    q = unpack_codes(W, bits)
+    Wdq = dequant_w32(q, scales, biases, group, affine)
+    y = matmul_f64(x, Wdq)
+    g, u = y[:, :ffn], y[:, ffn:2 * ffn]
+    return u * g / (1.0 + np.exp(-g))
+
+
+def fused_ffn_f32(x, W, scales, biases, ffn: int, group: int = 64, bits: int = 4, affine: bool = True) -> np.ndarray:
+    """The shader's own arithmetic: f32 dot products in word order, silu and product in f32, one f16 rounding
+    (fused_ffn.wgsl:126-131: `silu_gate = gate * (1 / (1 + exp(-gate)))`, `output = f16(up * silu_gate)`)."""
+    y = gemv_word_order_f32(x, W, scales, biases, group, bits, affine)
+    y = np.atleast_2d(y).astype(F32)
+    g, u = y[:, :ffn], y[:, ffn:2 * ffn]
+    one = F32(1.0)
+    silu = (g * (one / (one + np.exp(-g, dtype=F32)))).astype(F32)
+    return (u * silu).astype(F32).astype(F16)

@@ -210,3 +210,17 @@ def test_moe_block_small(oracle_c):
     oracle_c.moe_gemv_ref(mb["x"], *mb["gate"], ids, 128, 256, 64, 4, 0, 256, 256, 5 * 256, out.reshape(-1))
     assert zo.rel_err(out[..., :128], g, 1e-3) < 2e-3
     assert r["y"].shape == (3, 256) and np.isfinite(r["y"].astype(np.float32)).all()
+
+
+def test_fused_ffn_restatements_agree():
+    """fused_ffn.wgsl:63-131 restated twice (f64 anchor, the shader's f32 order): they agree to the output tolerance, and
+    the anchor is the plain matmul anchor followed by the activation."""
+    import zero_tvm_b200 as z
+    for affine, group in ((True, 64), (False, 32)):
+        p = z.synth.projection(96, 512, M=3, seed=8, group=group, affine=affine)
+        a = zo.fused_ffn_f64(p["x"], p["W"], p["scales"], p["biases"], 48, group, 4, affine)
+        b = zo.fused_ffn_f32(p["x"], p["W"], p["scales"], p["biases"], 48, group, 4, affine)
+        assert a.shape == b.shape == (3, 48)
+        assert zo.rel_err_scaled(b.astype(np.float64), a, 1e-3) <= 2e-3
+        y = zo.matmul_f64(p["x"], zo.dequant_w32(zo.unpack_codes(p["W"], 4), p["scales"], p["biases"], group, affine))
+        assert np.allclose(a, y[:, 48:] * y[:, :48] / (1 + np.exp(-y[:, :48])), rtol=1e-12)

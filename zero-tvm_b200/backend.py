@@ -321,6 +321,23 @@ class CudaMatmulBackend:
         vocab = self._experts_of(weights, 1, D * bits // 32)
         self.ctx.embedding_affine(D, bits, vocab, int(pod[0]), out, input_ids, scales, weights, biases, stream)
 
+    def dispatch_fused_ffn(self, entry: str, bindings: Sequence, D: int, ffn: int, m_rows: int = 1, stream=None):
+        """fused_ffn: [output, input, scales, weights, {packGridDimX}] with the reference's symmetric group-32 weights
+        (src/compiler/shaders/fused_ffn.wgsl:19-25; D and FFN_DIM are pipeline constants there); fused_ffn_affine:
+        [output, input, scales, weights, {…}, biases], group 64 -- the sibling the engine lacks
+        (src/zero-tvm/engine-core.ts:2513-2519). One workgroup per output in the reference: packGridDimX = ffn."""
+        if entry not in ("fused_ffn", "fused_ffn_affine"):
+            raise KeyError(f"no such fused FFN pipeline: {entry}")
+        affine = entry.endswith("_affine")
+        if len(bindings) < 5:
+            raise ValueError("bind group needs [output, input, scales, weights, PODArgs, ...]")
+        out, x, scales, weights = bindings[:4]
+        biases = bindings[5] if affine and len(bindings) > 5 else None
+        if affine and biases is None:
+            raise ValueError(f"{entry}: affine variants bind biases at slot 5")
+        desc = MmDesc(D, ffn, m_rows, 64 if affine else 32, 4, int(affine), 0)
+        self.ctx.fused_ffn(desc, out, x, scales, weights, biases, stream)
+
     # MoE glue, same argument order as the reference bind groups
     def moe_router_topk(self, ids, scores, logits, E: int, K: int, norm_topk: bool, has_shared: bool, tokens: int,
                         stream=None):

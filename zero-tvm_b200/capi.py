@@ -17,6 +17,7 @@ SYMBOLS = [
     "ztvm_version", "ztvm_status_string", "ztvm_init", "ztvm_destroy", "ztvm_last_error", "ztvm_sync",
     "ztvm_int4_matmul", "ztvm_int4_matmul_multi", "ztvm_int4_matmul_host", "ztvm_int4_matmul_moe", "ztvm_int4_matmul_moe_noalloc",
     "ztvm_moe_router_logits", "ztvm_embedding_affine", "ztvm_moe_plan_reuse", "ztvm_moe_route_topk", "ztvm_moe_dispatch_plan", "ztvm_moe_ep_dispatch", "ztvm_int4_matmul_moe_ep", "ztvm_silu_mul_rows",
+    "ztvm_fused_ffn",
     "ztvm_silu_mul",
     "ztvm_moe_combine", "ztvm_unpack_codes", "ztvm_unpack_codes_streamed", "ztvm_dequant", "ztvm_device_errors",
 ]
@@ -88,6 +89,7 @@ def load() -> C.CDLL:
         "ztvm_moe_ep_dispatch": [vp, C.POINTER(MoeEpLayout), vp, u32, u32, u32, u32, vp, u32, u32, vp],
         "ztvm_int4_matmul_moe_ep": [vp, C.POINTER(MoeDesc), C.POINTER(MoeEpRows), vp, vp, vp, vp, vp, vp, vp],
         "ztvm_silu_mul_rows": [vp, C.POINTER(MoeEpRows), u32, vp, vp, vp],
+        "ztvm_fused_ffn": [vp, C.POINTER(MmDesc), vp, vp, vp, vp, vp, vp],
         "ztvm_silu_mul": [vp, u32, u32, vp, vp, vp],
         "ztvm_moe_combine": [vp, u32, u32, u32, vp, vp, vp, vp],
         "ztvm_unpack_codes": [vp, C.POINTER(MmDesc), vp, vp, vp],
@@ -209,6 +211,11 @@ class Context:
 
     def silu_mul_rows(self, rows: MoeEpRows, ffn, h, gate_up, stream=None):
         check(self._lib.ztvm_silu_mul_rows(self.handle, C.byref(rows), ffn, ptr(h), ptr(gate_up), stream_ptr(stream)))
+
+    def fused_ffn(self, desc: MmDesc, h, x, scales, packed_w, biases=None, stream=None):
+        """h = f16(up * silu(gate)) for the [2 * desc.N, K] stack of gate and up rows (desc.N = ffn)."""
+        check(self._lib.ztvm_fused_ffn(self.handle, C.byref(desc), ptr(h), ptr(x), ptr(scales), ptr(packed_w), ptr(biases),
+                                       stream_ptr(stream)))
 
     def silu_mul(self, rows, ffn, h, gate_up, stream=None):
         check(self._lib.ztvm_silu_mul(self.handle, rows, ffn, ptr(h), ptr(gate_up), stream_ptr(stream)))

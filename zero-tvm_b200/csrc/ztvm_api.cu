@@ -27,6 +27,7 @@ struct ztvm_ctx {
   // plan scratch of the grouped MoE matmul (grown on demand: a call that needs more synchronises the device,
   // reallocates and goes on; make one call at the largest size before capturing a graph)
   void* d_ws; size_t d_ws_bytes;
+  void* d_ffn; size_t d_ffn_bytes;      // f32 gate/up rows of ztvm_fused_ffn's two-launch form
   // env ZTVM_MOE_GROUPED (a measurement knob): 0 forces the per-pair GEMV, 1 the tensor-core tiles, 2 the streaming
   // grouped kernel; unset = by size (below 128 pairs per-pair; then streaming while an expert sees few pairs)
   int moe_grouped;
@@ -221,6 +222,7 @@ ztvm_status ztvm_destroy(ztvm_ctx* ctx) {
   if (ctx->d_x) cudaFree(ctx->d_x);
   if (ctx->d_y) cudaFree(ctx->d_y);
   if (ctx->d_ws) cudaFree(ctx->d_ws);
+  if (ctx->d_ffn) cudaFree(ctx->d_ffn);
   cudaFree(ctx->err_counter);
   cudaStreamDestroy(ctx->stream);
   ctx->magic = 0;
@@ -266,6 +268,37 @@ ztvm_status ztvm_int4_matmul(ztvm_ctx* ctx, const ztvm_mm_desc* d, void* y, cons
     else if (use_mma(ctx, d, dd.M)) ZTVM_CUDA(ztvm::launch_gemv_mma(p, false, 1, 1, st));
     else ZTVM_CUDA(ztvm::launch_gemv(p, (int)d->bits, false, 1, 1, ctx->sm_count, st));
   }
+  return ZTVM_OK;
+}
+
+ztvm_status ztvm_fused_ffn(ztvm_ctx* ctx, const ztvm_mm_desc* d, void* h, const void* x, const void* scales,
+                           const void* packed_w, const void* biases, void* stream) {
+  ztvm_status s = check_ctx(ctx);
+  if (s) return s;
+  if ((s = check_desc(d, true))) return s;
+  if (d->out_f32) return fail(ZTVM_ERR_UNSUPPORTED, "the fused FFN stores f16");
+  if (d->N > 0x7FFFFFFFu) return fail(ZTVM_ERR_TOO_LARGE, "ffn=%u: 2 * ffn rows must fit 32 bits", d->N);
+  ztvm_mm_desc gu = *d;
+  gu.N = 2 * d->N;
+  if ((s = check_buffers(&gu, h, x, scales, packed_w, biases))) return s;
+  cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : ctx->stream;
+  if (d->M <= 8 && ctx->gemv_path == 0) {
+    ztvm::GemvParams p = gemv_params(&gu, h, x, scales, packed_w, biases);
+    p.pair_rows = d->N;
+    p.y_row_stride = d->N;
+    if (ztvm::gemv_tc_supported(p, (int)d->bits, ctx->sm_count)) {
+      ZTVM_CUDA(ztvm::launch_gemv_tc(p, ctx->sm_count, st));
+      return ZTVM_OK;
+    }
+  }
+  const size_t need = (size_t)d->M * gu.N * sizeof(float);
+  if (ctx->d_ffn_bytes < need) {
+    ZTVM_CUDA(cudaDeviceSynchronize());
+    if ((s = grow(&ctx->d_ffn, &ctx->d_ffn_bytes, need, false))) return s;
+  }
+  gu.out_f32 = 1;
+  if ((s = ztvm_int4_matmul(ctx, &gu, ctx->d_ffn, x, scales, packed_w, biases, st))) return s;
+  ZTVM_CUDA(ztvm::launch_silu_mul_f32(static_cast<const float*>(ctx->d_ffn), static_cast<__half*>(h), d->M, d->N, st));
   return ZTVM_OK;
 }
 

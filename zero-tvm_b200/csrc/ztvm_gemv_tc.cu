@@ -57,10 +57,27 @@ gemv_tc_kernel(const GemvParams p) {
   const bool warp_active = rg < RG;
   const uint32_t num_kt = (slices + KS - 1) / KS;
 
-  const uint32_t r0 = (uint32_t)((uint64_t)blockIdx.x * p.N / gridDim.x);
-  const uint32_t r1 = (uint32_t)((uint64_t)(blockIdx.x + 1) * p.N / gridDim.x);
-  const uint32_t nrows = r1 - r0;
-  const uint32_t ntiles = (nrows + 15) / 16;
+  // Rows of this CTA. Plain form: the contiguous rows [r0, r0 + nrows). Paired form (gate rows, then up rows, in one
+  // weight): the CTA owns output rows [r0, r0 + prows) and walks their gate and up tiles alternately -- tile 2j holds
+  // gate rows r0 + 16 j .., tile 2j + 1 the up rows pair_rows further down -- so that both halves of an output meet in
+  // the same block of rounds. `nrows` counts tile slots x 16 there.
+  const bool paired = p.pair_rows != 0u;
+  const uint32_t out_rows = paired ? p.pair_rows : p.N;
+  const uint32_t r0 = (uint32_t)((uint64_t)blockIdx.x * out_rows / gridDim.x);
+  const uint32_t r1 = (uint32_t)((uint64_t)(blockIdx.x + 1) * out_rows / gridDim.x);
+  const uint32_t prows = r1 - r0;
+  const uint32_t ntiles = paired ? 2u * ((prows + 15) / 16) : (prows + 15) / 16;
+  const uint32_t nrows = paired ? ntiles * 16u : prows;
+  // first weight row of the tile that starts at CTA-relative row `trow`, and how many of its 16 rows exist
+  auto tile_row = [&](uint32_t trow) -> uint32_t {
+    if (!paired) return r0 + trow;
+    const uint32_t t = trow >> 4;
+    return (t & 1u) * p.pair_rows + r0 + (t >> 1) * 16u;
+  };
+  auto tile_live = [&](uint32_t trow) -> uint32_t {
+    const uint32_t first = paired ? (trow >> 5) * 16u : trow;
+    return prows - first < 16u ? prows - first : 16u;
+  };
   uint32_t rounds = (ntiles + RG - 1) / RG;
   rounds = (rounds + kTcRounds - 1) / kTcRounds * kTcRounds;
   const uint32_t total = num_kt * rounds;                   // (K tile, round) steps of every warp
@@ -82,17 +99,18 @@ gemv_tc_kernel(const GemvParams p) {
       const uint32_t trow = (i_rd * RG + rg) * 16;          // first row of the tile, CTA-relative
       if (sl < slices && trow < nrows) {
         const uint32_t st = ring + (i_step % kTcDepth) * kTcTileBytes;
-        const uint32_t* src = p.W + (size_t)(r0 + trow + cp_row) * p.KP + sl * 32 + cp_chunk * 4;
-        const __half* sbp = (sb_which ? p.B : p.S) + (size_t)(r0 + trow + sb_row) * p.SPR + sl * 4;
-        if (trow + 16 <= nrows) {
+        const uint32_t wrow = tile_row(trow), live = tile_live(trow);
+        const uint32_t* src = p.W + (size_t)(wrow + cp_row) * p.KP + sl * 32 + cp_chunk * 4;
+        const __half* sbp = (sb_which ? p.B : p.S) + (size_t)(wrow + sb_row) * p.SPR + sl * 4;
+        if (live == 16u) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) tc_cp16(st + cp_dst + i * 512, src + i * row4);   // (row + 4i) & 3 == row & 3
           if (AFFINE || sb_which == 0) tc_cp8(st + sb_dst, sbp);
         } else {
 #pragma unroll
           for (int i = 0; i < 4; ++i)
-            if (trow + cp_row + 4 * i < nrows) tc_cp16(st + cp_dst + i * 512, src + i * row4);
-          if (trow + sb_row < nrows && (AFFINE || sb_which == 0)) tc_cp8(st + sb_dst, sbp);
+            if (cp_row + 4 * i < live) tc_cp16(st + cp_dst + i * 512, src + i * row4);
+          if (sb_row < live && (AFFINE || sb_which == 0)) tc_cp8(st + sb_dst, sbp);
         }
       }
     }
@@ -264,13 +282,26 @@ gemv_tc_kernel(const GemvParams p) {
         const uint32_t r16 = br & 15u, tb = br >> 4;
         const uint32_t q = tb / RG, rgi = tb - q * RG;
         const uint32_t row = ((blk * kTcRounds + q) * RG + rgi) * 16 + r16;
-        if (row >= nrows) continue;
+        if (row >= nrows || r16 >= tile_live(row & ~15u)) continue;
         float v = 0.f;
         for (uint32_t k2 = 0; k2 < KS; ++k2) v += buf[((size_t)(rgi * KS + k2) * kBlkRows + q * 16 + r16) * NT + tok];
         if (num_kt > 1) {
           float* a = acc_sm + (size_t)row * p.M + tok;
           if (kt) v += *a;
           if (kt + 1 < num_kt) { *a = v; continue; }
+        }
+        if (paired) {
+          // The thread that holds an up row (odd tile) finishes the output: the gate row's sum is one tile back, in the
+          // same block (tiles per block are even and blocks start on even tiles). Its own thread wrote nothing.
+          const uint32_t tile = row >> 4;
+          if ((tile & 1u) == 0u) continue;
+          const uint32_t tg = tb - 1u, qg = tg / RG, rgg = tg - qg * RG;
+          float gsum = 0.f;
+          for (uint32_t k2 = 0; k2 < KS; ++k2) gsum += buf[((size_t)(rgg * KS + k2) * kBlkRows + qg * 16 + r16) * NT + tok];
+          if (num_kt > 1 && kt) gsum += acc_sm[(size_t)(row - 16u) * p.M + tok];
+          const float silu = gsum * (1.0f / (1.0f + expf(-gsum)));
+          reinterpret_cast<__half*>(p.Y)[(size_t)tok * p.y_row_stride + r0 + (tile >> 1) * 16u + r16] = __float2half_rn(v * silu);
+          continue;
         }
         const size_t o = (size_t)tok * p.y_row_stride + r0 + row;
         if (p.out_f32) {
@@ -289,12 +320,20 @@ gemv_tc_kernel(const GemvParams p) {
 
 // ---- host side --------------------------------------------------------------------------------------------
 // Shared-memory accumulators (only when K spans several K tiles of W slices) must fit beside the ring.
+static unsigned tc_grid_for(const GemvParams& p, int sm_count) {
+  const uint32_t out_rows = p.pair_rows ? p.pair_rows : p.N;
+  return out_rows < (uint32_t)sm_count ? out_rows : (unsigned)sm_count;
+}
+// rows of the cross-K-tile accumulators of one CTA (paired form: gate and up tile slots, 16 rows each)
+static uint64_t tc_acc_rows(const GemvParams& p, unsigned grid) {
+  const uint32_t out_rows = p.pair_rows ? p.pair_rows : p.N;
+  const uint64_t rows = ((uint64_t)out_rows + grid - 1) / grid + 1;
+  return p.pair_rows ? 2 * ((rows + 15) / 16) * 16 : rows;
+}
 static bool tc_acc_fits(const GemvParams& p, int sm_count, int warps) {
   const uint32_t slices = p.K / kTcSlice;
   if (slices <= (uint32_t)warps) return true;
-  const uint32_t grid = p.N < (uint32_t)sm_count ? p.N : (uint32_t)sm_count;
-  const uint64_t rows = ((uint64_t)p.N + grid - 1) / grid + 1;
-  return rows * p.M * 4 <= (warps == 8 ? kTcMaxAccBytes / 2 : kTcMaxAccBytes);
+  return tc_acc_rows(p, tc_grid_for(p, sm_count)) * p.M * 4 <= (warps == 8 ? kTcMaxAccBytes / 2 : kTcMaxAccBytes);
 }
 // warps per CTA for a problem: 8 (two CTAs per SM) while an SM's share of the weights is small, else 16
 static int tc_warps_for(const GemvParams& p, int sm_count) {
@@ -305,12 +344,9 @@ static int tc_warps_for(const GemvParams& p, int sm_count) {
   if (w == 8 && !tc_acc_fits(p, sm_count, 8)) w = 16;
   return w;
 }
-static unsigned tc_grid_for(const GemvParams& p, int sm_count) {
-  return p.N < (uint32_t)sm_count ? p.N : (unsigned)sm_count;
-}
-
 bool gemv_tc_supported(const GemvParams& p, int bits, int sm_count) {
   if (bits != 4 || p.group_shift != 6 || p.M < 1 || p.M > 8) return false;
+  if (p.pair_rows && (p.N != 2 * p.pair_rows || p.out_f32 || p.n_more)) return false;
   if (p.K % kTcSlice || p.K == 0 || p.N == 0) return false;
   if (p.x_row_stride % 8 || (reinterpret_cast<uintptr_t>(p.X) & 15u)) return false;
   if ((reinterpret_cast<uintptr_t>(p.W) & 15u) || (reinterpret_cast<uintptr_t>(p.S) & 7u) ||
@@ -349,7 +385,7 @@ static cudaError_t launch_tc_w(const GemvParams& p, int sm_count, cudaStream_t s
   const unsigned grid = tc_grid_for(p, sm_count);
   const int nt = p.M == 1 ? 1 : p.M == 2 ? 2 : p.M <= 4 ? 4 : 8;
   size_t smem = (size_t)W * kTcDepth * kTcTileBytes + (size_t)2 * W * tc_rounds(nt) * 16 * nt * 4;
-  if (p.K / kTcSlice > (uint32_t)W) smem += (((size_t)p.N + grid - 1) / grid + 1) * p.M * 4;
+  if (p.K / kTcSlice > (uint32_t)W) smem += (size_t)tc_acc_rows(p, grid) * p.M * 4;
   const bool affine = p.B != nullptr;
   switch (nt) {
     case 1: return affine ? launch_tc_one<1, true, W>(p, grid, smem, st) : launch_tc_one<1, false, W>(p, grid, smem, st);

@@ -377,6 +377,22 @@ cudaError_t launch_silu_mul(const __half* gate_up, __half* h, uint32_t rows, uin
   return cudaGetLastError();
 }
 
+// The same over f32 [gate(ffn) | up(ffn)] rows: the second step of the fused FFN on shapes the paired GEMV does not
+// take (fused_ffn.wgsl keeps both dot products in f32 up to the final store).
+__global__ void silu_mul_f32_kernel(const float* __restrict__ gate_up, __half* __restrict__ h, uint32_t rows, uint32_t ffn) {
+  const size_t total = (size_t)rows * ffn;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / ffn, c = i - r * ffn;
+    h[i] = __float2half_rn(silu_mul_one(gate_up[r * 2 * ffn + c], gate_up[r * 2 * ffn + ffn + c]));
+  }
+}
+cudaError_t launch_silu_mul_f32(const float* gate_up, __half* h, uint32_t rows, uint32_t ffn, cudaStream_t st) {
+  const size_t total = (size_t)rows * ffn;
+  if (total == 0) return cudaSuccess;
+  silu_mul_f32_kernel<<<grid_for(total, 256), 256, 0, st>>>(gate_up, h, rows, ffn);
+  return cudaGetLastError();
+}
+
 // ---- weighted combine -----------------------------------------------------------------------------
 // out[t][i] = f16(sum_s score[t][s] * f32(y[t][s][i])), slots added in index order (moe_combine.wgsl:39-43).
 template <int VEC>

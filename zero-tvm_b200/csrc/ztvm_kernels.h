@@ -34,6 +34,10 @@ struct GemvParams {
   uint32_t seg_cap;
   const uint32_t* dst_index;
   void* y_seg[9];
+  // Fused gate/up form of the persistent GEMV (fused_ffn.wgsl): the weight holds 2 * pair_rows rows, gate rows first
+  // and up rows after them; the output has pair_rows columns, y[i] = f16(up[i] * silu(gate[i])) with both dot products
+  // and the activation in f32. 0 = plain matmul.
+  uint32_t pair_rows;
 };
 
 cudaError_t launch_gemv(GemvParams p, int bits, bool moe, uint32_t tokens, uint32_t slots, int sm_count,
@@ -123,6 +127,7 @@ cudaError_t launch_route_topk(const float* logits, uint32_t* ids, float* scores,
 // seg_counts != nullptr: rows come in regions of seg_cap, only the first seg_counts[region] of each are computed
 cudaError_t launch_silu_mul(const __half* gate_up, __half* h, uint32_t rows, uint32_t ffn, cudaStream_t st,
                             const uint32_t* seg_counts = nullptr, uint32_t seg_cap = 1);
+cudaError_t launch_silu_mul_f32(const float* gate_up, __half* h, uint32_t rows, uint32_t ffn, cudaStream_t st);
 cudaError_t launch_moe_combine(const __half* y_slots, const float* scores, __half* out, uint32_t tokens,
                                uint32_t slots, uint32_t d, cudaStream_t st);
 
