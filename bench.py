@@ -630,7 +630,7 @@ def main():
     shapes = workload_shapes(args.workload)
     if BITS != 4:
         args.no_cpu_baseline = True     # the CPU sample is the 4-bit reference-order matmul
-    is_gemm = shapes[0][3] > 8
+    is_gemm = shapes[0][3] > 16      # up to 16 rows the library runs GEMV slabs (f32 weights)
     sets, R = make_sets(shapes, 1234 + rank, torch, device)
     xs = [torch.randn((M, K), device=device).to(torch.float16) for _, N, K, M, _ in shapes]
     descs = [z.MmDesc(K, N, M, 64, BITS, 1, int(f32)) for _, N, K, M, f32 in shapes]

@@ -90,7 +90,8 @@ typedef struct ztvm_mm_desc {
  * int4_matmul_batched_dyn[_affine] and the tiled / subgroup-matrix prefill GEMMs
  * (src/compiler/shaders/int4_matmul.gen.ts:170-571, :580-695, :805-1456; call sites
  * src/zero-tvm/engine-core.ts:2290, :2312, :2517-2519, :2543-2549, :4280-4293).
- * M <= 8 runs the bandwidth-bound GEMV; larger M runs the tensor-core GEMM. */
+ * M <= 8 runs the bandwidth-bound GEMV, M <= 16 two slabs of it; larger M runs the tensor-core GEMM (which multiplies
+ * f16-rounded weights f16(s*q+b), like the reference's matrix-unit GEMMs). */
 ZTVM_API ztvm_status ztvm_int4_matmul(ztvm_ctx* ctx, const ztvm_mm_desc* desc, void* y, const void* x,
                              const void* scales, const void* packed_w, const void* biases, void* stream);
 

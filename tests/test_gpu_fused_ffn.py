@@ -54,7 +54,7 @@ def test_two_launch_form_on_other_shapes(group, bits, affine, M, backend, dev):
     ffn, K = 384, 1024 if bits != 3 else 768
     p = z.synth.projection(2 * ffn, K, M=M, seed=group + bits + M, bits=bits, group=group, affine=affine)
     got = run_fused(backend, dev, p, ffn, M).astype(np.float64)
-    w16 = M > 8 and bits == 4                      # the tensor-core GEMM multiplies f16-rounded weights
+    w16 = M > 16 and bits == 4                     # the tensor-core GEMM multiplies f16-rounded weights
     q = zo.unpack_codes(p["W"], bits)
     Wdq = (zo.dequant_w16 if w16 else zo.dequant_w32)(q, p["scales"], p["biases"], group, affine)
     y = zo.matmul_f64(p["x"], Wdq)

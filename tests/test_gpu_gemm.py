@@ -33,9 +33,10 @@ def run_gemm(backend, dev, p, entry=None, extra_rows=0):
 
 
 def check(y, p, oracle_c):
-    y64 = oracle_c.matmul_f64(p["x"], p["W"], p["scales"], p["biases"], p["group"], 4, p["affine"], w16=True)
+    gemm = y.shape[0] > 16     # up to 16 rows the call runs as GEMV slabs: f32 weights, the GEMV floor
+    y64 = oracle_c.matmul_f64(p["x"], p["W"], p["scales"], p["biases"], p["group"], 4, p["affine"], w16=gemm)
     assert np.isfinite(y).all()
-    err = zo.rel_err_scaled(y, y64, FLOOR_FRAC)
+    err = zo.rel_err_scaled(y, y64, FLOOR_FRAC if gemm else 1e-3)
     record_parity(err, zo.rel_err(y, y64))     # floored and pure-relative error, listed at the end of the run
     assert err <= TOL, f"rel err {err:.3e} (floor 1e-3 rms: {zo.rel_err_scaled(y, y64):.3e})"
     return err
@@ -51,7 +52,7 @@ def test_prefill_gemm_config(M, backend, dev, oracle_c):
     check(y, p, oracle_c)
 
 
-@pytest.mark.parametrize("M,N,K", [(13, 96, 128), (9, 8, 64), (100, 1000, 1408), (129, 72, 192), (300, 4096, 4096),
+@pytest.mark.parametrize("M,N,K", [(13, 96, 128), (9, 8, 64), (17, 96, 128), (31, 40, 320), (100, 1000, 1408), (129, 72, 192), (300, 4096, 4096),
                                    (257, 130, 768)])
 def test_ragged_shapes(M, N, K, backend, dev, oracle_c):
     """13 x 96 x 128 is the reference's own GEMM gate (scripts/gemm-bench.mjs:483-498). Rows past M stay untouched."""

@@ -36,7 +36,7 @@ def check_y(y, p, oracle_c, w16=None, tol=TOL):
     """M <= 8 runs the GEMV (f32 weights, fp64 anchor over W32, floor 1e-3 of the output rms); more rows of 4-bit
     weights run the tensor-core GEMM (f16 weights: anchor over W16, graded with the GEMM floor of 1e-2 rms)."""
     if w16 is None:
-        w16 = y.shape[0] > 8 and p["bits"] == 4
+        w16 = y.shape[0] > 16 and p["bits"] == 4
     y64 = oracle_c.matmul_f64(p["x"], p["W"], p["scales"], p["biases"], p["group"], p["bits"], p["affine"], w16=w16)
     assert np.isfinite(y).all(), "output holds NaN/inf (poison not overwritten?)"
     assert np.abs(y).max() > 0

@@ -244,7 +244,11 @@ ztvm_status ztvm_int4_matmul(ztvm_ctx* ctx, const ztvm_mm_desc* d, void* y, cons
   if ((s = check_desc(d, true))) return s;
   if ((s = check_buffers(d, y, x, scales, packed_w, biases))) return s;
   cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : ctx->stream;
-  if (d->M > 8 && ztvm::gemm_w4_supported((int)d->bits, d->group, d->K) && !ctx->no_gemm) {
+  // Up to 16 rows the GEMV in slabs of eight wins: it re-streams the weights once per slab at HBM speed, while the
+  // tensor-core kernels dequantise every code once at ~12 codes per clock and SM whatever M is (measured on
+  // 8192 x 2048: 9.4 us against 21 us at M = 16, 14 against 13 us at M = 24). It is also the reference's choice for
+  // short chunks (runtime-M matvec, exact codes and f32 weights; its GEMMs start at 64 rows).
+  if (d->M > 16 && ztvm::gemm_w4_supported((int)d->bits, d->group, d->K) && !ctx->no_gemm) {
     if (!aligned(y, 16)) return fail(ZTVM_ERR_ALIGNMENT, "y must be 16-byte aligned for the GEMM path");
     // M > 128: weights as the A operand in tensor memory (256 tokens per instruction); up to 128 rows the tiles with
     // both operands in shared memory, whose 64-row weight tiles give twice as many CTAs
