@@ -113,6 +113,16 @@ ZTVM_API ztvm_status ztvm_int4_matmul_multi(ztvm_ctx* ctx, const ztvm_mm_desc* d
 ZTVM_API ztvm_status ztvm_int4_matmul_host(ztvm_ctx* ctx, const ztvm_mm_desc* desc, void* y_host, const void* x_host,
                                   const void* scales, const void* packed_w, const void* biases);
 
+/* The host-buffer call without the wait, for callers that stream many matmuls: copy-in, matmul and copy-out are
+ * queued on one of three internal lanes (round robin) and the call returns. Calls on different lanes overlap -- one
+ * lane's kernel runs while another's activations arrive and a third's results leave. x_host and y_host must be
+ * page-locked (else ZTVM_ERR_UNSUPPORTED) and belong to the call until ztvm_host_wait returns; calls in flight need
+ * distinct y_host buffers. No counterpart in the reference (its activations never leave the device). */
+ZTVM_API ztvm_status ztvm_int4_matmul_host_async(ztvm_ctx* ctx, const ztvm_mm_desc* desc, void* y_host, const void* x_host,
+                                        const void* scales, const void* packed_w, const void* biases);
+/* Waits for every ztvm_int4_matmul_host_async call made so far. */
+ZTVM_API ztvm_status ztvm_host_wait(ztvm_ctx* ctx);
+
 /* The MoE PODArgs (src/compiler/shaders/int4_matmul.gen.ts:216-225; built at
  * src/zero-tvm/engine-core.ts:1049-1056). Strides are in ELEMENTS of x / y. mm.M must be 1. */
 typedef struct ztvm_moe_desc {

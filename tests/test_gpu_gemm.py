@@ -118,3 +118,28 @@ def test_f32_output_through_the_c_abi(M, backend, dev, oracle_c):
     assert backend.ctx.device_errors() == 0
     assert (out[M:] == -77.0).all()
     check(out[:M], p, oracle_c)
+
+
+def test_pipelined_host_calls_equal_the_synchronous_one(backend, dev):
+    """ztvm_int4_matmul_host_async on its three lanes, more calls than lanes, different activations per call: every result
+    equals the synchronous host call's bit for bit; pageable buffers are refused."""
+    import torch
+    M, N, K = 40, 256, 512
+    p = z.synth.projection(N, K, M=M, seed=21)
+    s, W, b = dev.put(p["scales"]), dev.put(p["W"]), dev.put(p["biases"])
+    d = z.MmDesc(K, N, M, 64, 4, 1, 0)
+    rng = np.random.default_rng(4)
+    xs = [torch.from_numpy(z.synth.make_x(rng, M, K)).pin_memory() for _ in range(7)]
+    ys = [torch.empty((M, N), dtype=torch.float16).pin_memory() for _ in range(7)]
+    ref = [torch.empty((M, N), dtype=torch.float16).pin_memory() for _ in range(7)]
+    for x, y in zip(xs, ref):
+        backend.ctx.int4_matmul_host(d, y, x, s, W, b)
+    for x, y in zip(xs, ys):
+        backend.ctx.int4_matmul_host_async(d, y, x, s, W, b)
+    backend.ctx.host_wait()
+    for i in range(7):
+        assert torch.equal(ys[i], ref[i]), i
+    assert not torch.equal(ref[0], ref[1])
+    with pytest.raises(z.ZtvmError) as e:
+        backend.ctx.int4_matmul_host_async(d, torch.empty((M, N), dtype=torch.float16), xs[0], s, W, b)
+    assert e.value.status == z.capi.ERR_UNSUPPORTED and "page-locked" in str(e.value)

@@ -15,7 +15,7 @@ LIB_PATH = os.environ.get("ZTVM_LIB") or os.path.join(_HERE, "lib", "libztvm_b20
 # every symbol include/ztvm_b200.h declares
 SYMBOLS = [
     "ztvm_version", "ztvm_status_string", "ztvm_init", "ztvm_destroy", "ztvm_last_error", "ztvm_sync",
-    "ztvm_int4_matmul", "ztvm_int4_matmul_multi", "ztvm_int4_matmul_host", "ztvm_int4_matmul_moe", "ztvm_int4_matmul_moe_noalloc",
+    "ztvm_int4_matmul", "ztvm_int4_matmul_multi", "ztvm_int4_matmul_host", "ztvm_int4_matmul_host_async", "ztvm_host_wait", "ztvm_int4_matmul_moe", "ztvm_int4_matmul_moe_noalloc",
     "ztvm_moe_router_logits", "ztvm_embedding_affine", "ztvm_moe_plan_reuse", "ztvm_moe_route_topk", "ztvm_moe_dispatch_plan", "ztvm_moe_ep_dispatch", "ztvm_int4_matmul_moe_ep", "ztvm_silu_mul_rows",
     "ztvm_fused_ffn",
     "ztvm_silu_mul",
@@ -79,6 +79,8 @@ def load() -> C.CDLL:
         "ztvm_int4_matmul": [vp, C.POINTER(MmDesc), vp, vp, vp, vp, vp, vp],
         "ztvm_int4_matmul_multi": [vp, C.POINTER(MmDesc), C.POINTER(C.c_void_p), u32, u32, vp, vp, vp, vp, vp],
         "ztvm_int4_matmul_host": [vp, C.POINTER(MmDesc), vp, vp, vp, vp, vp],
+        "ztvm_int4_matmul_host_async": [vp, C.POINTER(MmDesc), vp, vp, vp, vp, vp],
+        "ztvm_host_wait": [vp],
         "ztvm_int4_matmul_moe": [vp, C.POINTER(MoeDesc), vp, vp, vp, vp, vp, vp, vp],
         "ztvm_int4_matmul_moe_noalloc": [vp, C.POINTER(MoeDesc), vp, vp, vp, vp, vp, vp, vp],
         "ztvm_moe_router_logits": [vp, u32, u32, u32, u32, vp, vp, vp, vp, vp, vp],
@@ -159,6 +161,14 @@ class Context:
     def int4_matmul(self, desc: MmDesc, y, x, scales, packed_w, biases=None, stream=None):
         check(self._lib.ztvm_int4_matmul(self.handle, C.byref(desc), ptr(y), ptr(x), ptr(scales), ptr(packed_w),
                                          ptr(biases), stream_ptr(stream)))
+
+    def int4_matmul_host_async(self, desc: MmDesc, y_host, x_host, scales, packed_w, biases=None):
+        """Queued form of int4_matmul_host (page-locked buffers, three lanes round robin); host_wait() completes them."""
+        check(self._lib.ztvm_int4_matmul_host_async(self.handle, C.byref(desc), ptr(y_host), ptr(x_host), ptr(scales),
+                                                    ptr(packed_w), ptr(biases)))
+
+    def host_wait(self):
+        check(self._lib.ztvm_host_wait(self.handle))
 
     def int4_matmul_host(self, desc: MmDesc, y_host, x_host, scales, packed_w, biases=None):
         check(self._lib.ztvm_int4_matmul_host(self.handle, C.byref(desc), ptr(y_host), ptr(x_host), ptr(scales),

@@ -23,6 +23,9 @@ struct ztvm_ctx {
   // staging for the host-buffer entry point (grown on demand, freed at destroy)
   void* h_pinned; size_t h_pinned_bytes;
   void* d_x; size_t d_x_bytes;
+  // lanes of ztvm_int4_matmul_host_async: a stream and device buffers each, used round robin
+  struct HostLane { cudaStream_t stream; void* d_x; size_t d_x_bytes; void* d_y; size_t d_y_bytes; } lanes[3];
+  uint32_t next_lane;
   void* d_y; size_t d_y_bytes;
   // plan scratch of the grouped MoE matmul (grown on demand: a call that needs more synchronises the device,
   // reallocates and goes on; make one call at the largest size before capturing a graph)
@@ -223,6 +226,11 @@ ztvm_status ztvm_destroy(ztvm_ctx* ctx) {
   if (ctx->d_y) cudaFree(ctx->d_y);
   if (ctx->d_ws) cudaFree(ctx->d_ws);
   if (ctx->d_ffn) cudaFree(ctx->d_ffn);
+  for (auto& l : ctx->lanes) {
+    if (l.stream) { cudaStreamSynchronize(l.stream); cudaStreamDestroy(l.stream); }
+    if (l.d_x) cudaFree(l.d_x);
+    if (l.d_y) cudaFree(l.d_y);
+  }
   cudaFree(ctx->err_counter);
   cudaStreamDestroy(ctx->stream);
   ctx->magic = 0;
@@ -399,6 +407,40 @@ ztvm_status ztvm_int4_matmul_host(ztvm_ctx* ctx, const ztvm_mm_desc* d, void* y_
   ZTVM_CUDA(cudaMemcpyAsync(y_dst, ctx->d_y, yb, cudaMemcpyDeviceToHost, ctx->stream));
   ZTVM_CUDA(cudaStreamSynchronize(ctx->stream));
   if (!y_pinned) memcpy(y_host, y_dst, yb);
+  return ZTVM_OK;
+}
+
+// The host-buffer call without the wait: copy-in, matmul and copy-out are queued on one of three lanes (a stream and a
+// pair of device buffers each), taken round robin, so that while one call's kernel runs the next call's activations
+// arrive and the previous call's results leave (the two copy directions and the SMs work at the same time).
+ztvm_status ztvm_int4_matmul_host_async(ztvm_ctx* ctx, const ztvm_mm_desc* d, void* y_host, const void* x_host,
+                                        const void* scales, const void* packed_w, const void* biases) {
+  ztvm_status s = check_ctx(ctx);
+  if (s) return s;
+  if ((s = check_desc(d, true))) return s;
+  if (!y_host || !x_host) return fail(ZTVM_ERR_NULL_POINTER, "y_host/x_host must be non-NULL");
+  if (!host_is_pinned(x_host) || !host_is_pinned(y_host))
+    return fail(ZTVM_ERR_UNSUPPORTED, "the asynchronous host form copies straight from / to the caller's buffers: they must be page-locked");
+  const size_t xb = (size_t)d->M * d->K * 2, yb = (size_t)d->M * d->N * (d->out_f32 ? 4 : 2);
+  ztvm_ctx::HostLane& l = ctx->lanes[ctx->next_lane];
+  ctx->next_lane = (ctx->next_lane + 1u) % 3u;
+  if (!l.stream) ZTVM_CUDA(cudaStreamCreateWithFlags(&l.stream, cudaStreamNonBlocking));
+  if (l.d_x_bytes < xb || l.d_y_bytes < yb) {
+    ZTVM_CUDA(cudaStreamSynchronize(l.stream));      // the lane's earlier calls still use its buffers
+    if ((s = grow(&l.d_x, &l.d_x_bytes, xb, false))) return s;
+    if ((s = grow(&l.d_y, &l.d_y_bytes, yb, false))) return s;
+  }
+  ZTVM_CUDA(cudaMemcpyAsync(l.d_x, x_host, xb, cudaMemcpyHostToDevice, l.stream));
+  if ((s = ztvm_int4_matmul(ctx, d, l.d_y, l.d_x, scales, packed_w, biases, l.stream))) return s;
+  ZTVM_CUDA(cudaMemcpyAsync(y_host, l.d_y, yb, cudaMemcpyDeviceToHost, l.stream));
+  return ZTVM_OK;
+}
+
+ztvm_status ztvm_host_wait(ztvm_ctx* ctx) {
+  ztvm_status s = check_ctx(ctx);
+  if (s) return s;
+  for (auto& l : ctx->lanes)
+    if (l.stream) ZTVM_CUDA(cudaStreamSynchronize(l.stream));
   return ZTVM_OK;
 }
 
