@@ -375,7 +375,7 @@ class ShardedBench:
                 "clocks": clocks, "verified": verified}
 
     # -- experts over the ranks ---------------------------------------------------------------------------------------
-    def moe_ep(self, tokens, scaling):
+    def moe_ep(self, tokens, scaling, one_call=False):
         torch, sharded, world, rank = self.torch, self.sharded, self.world, self.rank
         E, top_k, d, ffn = 256, 8, 2048, 512
         epr = E // world
@@ -388,7 +388,7 @@ class ShardedBench:
             stacks.append((W[sel].contiguous(), sc[sel].contiguous(), b[sel].contiguous()))
             full.append((W, sc, b) if rank == 0 else None)
             del W, sc, b
-        moe = sharded.ExpertParallelMoE(self.k, *stacks, E=E, top_k=top_k, d=d, ffn=ffn, max_tokens=None)
+        moe = sharded.ExpertParallelMoE(self.k, *stacks, E=E, top_k=top_k, d=d, ffn=ffn, max_tokens=None, one_call=one_call)
         tl = tokens if scaling == "weak" else max(1, tokens // world)
         # the same token stream on every rank; each takes its slice (so rank 0 can check its slice against the oracle)
         gx = torch.Generator(device=self.device)
@@ -433,7 +433,8 @@ class ShardedBench:
         t_roof = max(t_hbm, t_tc, t_nv)
         bound = "hbm" if t_roof == t_hbm else "tensor" if t_roof == t_tc else "nvlink"
         return {"workload": "moe_ep", "tokens": T_total, "tokens_per_rank": tl, "scaling": scaling, "experts": E, "top_k": top_k,
-                "hidden": d, "ffn": ffn, "ms_per_step": ms, "value": tf, "unit": "TFLOP/s", "launch": how, "form": moe.form,
+                "hidden": d, "ffn": ffn, "ms_per_step": ms, "value": tf, "unit": "TFLOP/s", "launch": how,
+                "form": moe.form + (" (one ztvm_moe_ffn_ep call per step, the library's device-side barrier)" if moe.one_call else ""),
                 "roofline": {"bound": bound, "achieved": tf, "peak": self.peaks["tf_burst"] * world, "unit": "TFLOP/s",
                              "frac": t_roof / (ms * 1e-3), "roof_us": t_roof * 1e6,
                              "hbm_us": t_hbm * 1e6, "tensor_us": t_tc * 1e6, "nvlink_us": t_nv * 1e6, "traffic": None,
@@ -802,11 +803,12 @@ def main():
         sb = ShardedBench(torch, dist, z, rank, world, local, min(args.steps, 20), args.warmup)
         sharded_list = []
         for fn, a in ((sb.moe_ep, (2048, "strong")), (sb.moe_ep, (256, "strong")), (sb.moe_ep, (2048, "weak")),
+                      (sb.moe_ep, (2048, "strong", True)),
                       (sb.layer_set, (1, "fused")), (sb.layer_set, (4, "fused")), (sb.layer_set, (1, "nccl"))):
             if world == 1 and a == (1, "nccl"):
                 continue                      # one rank: no gather of either kind
-            if world == 1 and a == (2048, "weak"):
-                continue                      # one rank: weak and strong are the same run
+            if world == 1 and a in ((2048, "weak"), (2048, "strong", True)):
+                continue                      # one rank: weak and strong are the same run; nothing to dispatch
             try:
                 sharded_list.append(fn(*a))
             except Exception as e:            # a form that fails must not take the headline line with it

@@ -267,6 +267,35 @@ ZTVM_API ztvm_status ztvm_int4_matmul_moe_ep(ztvm_ctx* ctx, const ztvm_moe_desc*
 ZTVM_API ztvm_status ztvm_silu_mul_rows(ztvm_ctx* ctx, const ztvm_moe_ep_rows* rows, uint32_t ffn, void* h, const void* gate_up,
                                void* stream);
 
+/* Device-side barrier between the ranks of a sharded form, for hosts without one of their own. flags[r] = rank r's
+ * flag words as mapped in this process, u32[world + 1], zero before the first use (entry `rank` is this rank's own).
+ * The kernel bumps this rank's epoch (word `world` of its own array), stores it into word `rank` of every rank's array
+ * and waits until every word of its own array has reached the epoch: whatever a rank queued on its stream before its
+ * call -- stores to peer memory included -- is visible to a peer's work queued after that peer's call. Every rank makes
+ * the same sequence of calls on the same flag arrays. Stream-ordered and capturable; the wait is bounded (about a
+ * second), an expired wait is reported by ztvm_device_errors. No counterpart in the reference (one device). */
+ZTVM_API ztvm_status ztvm_peer_barrier(ztvm_ctx* ctx, uint32_t* const* flags, uint32_t world, uint32_t rank, void* stream);
+
+/* One expert-parallel FFN step in one call: ztvm_moe_ep_dispatch, barrier, gate and up projections and SiLU over what
+ * arrived, down projection storing every result row into its source rank's y_slots, barrier. Afterwards y_slots of
+ * this rank holds [tokens][top_k + has_shared][d] for its own tokens (ztvm_moe_combine finishes the block).
+ * ids come from ztvm_moe_route_topk. Stacks are this rank's: experts_per_rank experts (+ the shared expert last when
+ * has_shared). gate_up and h are scratch for (world + 1) * seg_cap rows. */
+typedef struct ztvm_moe_ffn_ep_args {
+  ztvm_moe_ep_layout layout;
+  uint32_t tokens, top_k, has_shared, ids_stride, d, ffn, x_tok_stride;
+  const uint32_t* ids;
+  const void* x;
+  const void* gate_w; const void* gate_scales; const void* gate_biases;   /* [experts][ffn][...], K = d */
+  const void* up_w; const void* up_scales; const void* up_biases;
+  const void* down_w; const void* down_scales; const void* down_biases;   /* [experts][d][...], K = ffn */
+  void* gate_up;            /* f16 [(world + 1) * seg_cap][2 * ffn] */
+  void* h;                  /* f16 [(world + 1) * seg_cap][ffn] */
+  void* y_slots[8];         /* every rank's result buffer f16 [tokens_r][top_k + has_shared][d], as mapped here */
+  uint32_t* flags[8];       /* ztvm_peer_barrier flag words of every rank */
+} ztvm_moe_ffn_ep_args;
+ZTVM_API ztvm_status ztvm_moe_ffn_ep(ztvm_ctx* ctx, const ztvm_moe_ffn_ep_args* args, void* stream);
+
 /* Fused FFN front half: h[m][i] = f16(up_i * gate_i / (1 + exp(-gate_i))) with gate_i = x[m] . W[i], up_i = x[m] . W[ffn + i],
  * both dot products and the activation in f32, one rounding at the store. `desc->N` is ffn (the output width); the
  * weight, scales and biases hold 2 * ffn rows, gate rows first. Replaces fused_ffn (src/compiler/shaders/fused_ffn.wgsl:

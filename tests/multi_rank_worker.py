@@ -4,7 +4,8 @@ stores). Every rank checks its own results against the oracle and exits non-zero
   row-sharded projection, fused form: a consumer kernel reads the output of forward n AFTER forward n+1 has been
     issued (the longest lifetime the class promises), while the ranks are deliberately driven out of step, so a
     buffer that a fast peer overwrites too early shows up as a wrong sum;
-  expert-parallel MoE block, peer-store form: eager and as a replayed CUDA graph against the oracle's whole block.
+  expert-parallel MoE block, peer-store form: eager and as a replayed CUDA graph against the oracle's whole block,
+    through the separate calls (torch's symmetric-memory barrier) and through ztvm_moe_ffn_ep (the library's barrier).
 """
 import os
 import sys
@@ -61,7 +62,7 @@ def projection_with_a_late_consumer(k, dev, rank, world):
     return worst
 
 
-def moe_block_by_peer_stores(k, dev, rank, world):
+def moe_block_by_peer_stores(k, dev, rank, world, one_call=False):
     E, top_k, d, ffn, tl = 16, 4, 256, 128, 40
     epr = E // world
     g = torch.Generator(device=dev)
@@ -72,7 +73,7 @@ def moe_block_by_peer_stores(k, dev, rank, world):
         t = rand_w(g, dev, (E + 1,), N, K)
         stacks.append(tuple(a[sel].contiguous() for a in t))
         full.append(np_w(t))
-    moe = sharded.ExpertParallelMoE(k, *stacks, E=E, top_k=top_k, d=d, ffn=ffn)
+    moe = sharded.ExpertParallelMoE(k, *stacks, E=E, top_k=top_k, d=d, ffn=ffn, one_call=one_call)
     x_all = torch.randn((tl * world, d), device=dev, generator=g).to(torch.float16)
     l_all = torch.randn((tl * world, E + 1), device=dev, generator=g)
     x, logits = x_all[rank * tl:(rank + 1) * tl].contiguous(), l_all[rank * tl:(rank + 1) * tl].contiguous()
@@ -116,6 +117,9 @@ def main():
     k = sharded.CudaKernels(be)
     a = projection_with_a_late_consumer(k, dev, rank, world)
     b = moe_block_by_peer_stores(k, dev, rank, world)
+    # the same step as ONE library call per rank (ztvm_moe_ffn_ep) with the library's own device-side barrier
+    c = moe_block_by_peer_stores(k, dev, rank, world, one_call=True)
+    b = max(b, c)
     assert be.ctx.device_errors() == 0
     print(f"rank {rank}: projection {a:.3e} moe {b:.3e} ok", flush=True)
     be.close()

@@ -13,7 +13,7 @@ There is no CPU implementation: importing is cheap, but creating a Context witho
 library or without a B200 raises.
 """
 from . import capi, synth  # noqa: F401
-from .capi import Context, MmDesc, MoeDesc, MoeEpLayout, MoeEpRows, ZtvmError  # noqa: F401
+from .capi import Context, MmDesc, MoeDesc, MoeEpLayout, MoeEpRows, MoeFfnEpArgs, ZtvmError  # noqa: F401
 from . import backend  # noqa: F401
 from . import sharded  # noqa: F401,E402
 from . import build  # noqa: F401,E402

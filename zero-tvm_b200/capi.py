@@ -16,7 +16,7 @@ LIB_PATH = os.environ.get("ZTVM_LIB") or os.path.join(_HERE, "lib", "libztvm_b20
 SYMBOLS = [
     "ztvm_version", "ztvm_status_string", "ztvm_init", "ztvm_destroy", "ztvm_last_error", "ztvm_sync",
     "ztvm_int4_matmul", "ztvm_int4_matmul_multi", "ztvm_int4_matmul_host", "ztvm_int4_matmul_host_async", "ztvm_host_wait", "ztvm_int4_matmul_moe", "ztvm_int4_matmul_moe_noalloc",
-    "ztvm_moe_router_logits", "ztvm_embedding_affine", "ztvm_moe_plan_reuse", "ztvm_moe_route_topk", "ztvm_moe_dispatch_plan", "ztvm_moe_ep_dispatch", "ztvm_int4_matmul_moe_ep", "ztvm_silu_mul_rows",
+    "ztvm_moe_router_logits", "ztvm_embedding_affine", "ztvm_moe_plan_reuse", "ztvm_moe_route_topk", "ztvm_moe_dispatch_plan", "ztvm_moe_ep_dispatch", "ztvm_int4_matmul_moe_ep", "ztvm_silu_mul_rows", "ztvm_peer_barrier", "ztvm_moe_ffn_ep",
     "ztvm_fused_ffn",
     "ztvm_silu_mul",
     "ztvm_moe_combine", "ztvm_unpack_codes", "ztvm_unpack_codes_streamed", "ztvm_dequant", "ztvm_device_errors",
@@ -46,6 +46,14 @@ class MoeEpLayout(C.Structure):
     _fields_ = [(n, C.c_uint32) for n in ("world", "rank", "experts_per_rank", "seg_cap")] + [
         ("recv_x", C.c_void_p * 8), ("recv_ids", C.c_void_p * 8), ("recv_src", C.c_void_p * 8), ("recv_cnt", C.c_void_p * 8),
         ("cursors", C.c_void_p)]
+
+
+class MoeFfnEpArgs(C.Structure):
+    """One expert-parallel FFN step (include/ztvm_b200.h: ztvm_moe_ffn_ep_args)."""
+    _fields_ = [("layout", MoeEpLayout)] + [(n, C.c_uint32) for n in (
+        "tokens", "top_k", "has_shared", "ids_stride", "d", "ffn", "x_tok_stride")] + [(n, C.c_void_p) for n in (
+        "ids", "x", "gate_w", "gate_scales", "gate_biases", "up_w", "up_scales", "up_biases", "down_w", "down_scales",
+        "down_biases", "gate_up", "h")] + [("y_slots", C.c_void_p * 8), ("flags", C.c_void_p * 8)]
 
 
 class MoeEpRows(C.Structure):
@@ -91,6 +99,8 @@ def load() -> C.CDLL:
         "ztvm_moe_ep_dispatch": [vp, C.POINTER(MoeEpLayout), vp, u32, u32, u32, u32, vp, u32, u32, vp],
         "ztvm_int4_matmul_moe_ep": [vp, C.POINTER(MoeDesc), C.POINTER(MoeEpRows), vp, vp, vp, vp, vp, vp, vp],
         "ztvm_silu_mul_rows": [vp, C.POINTER(MoeEpRows), u32, vp, vp, vp],
+        "ztvm_peer_barrier": [vp, C.POINTER(C.c_void_p), u32, u32, vp],
+        "ztvm_moe_ffn_ep": [vp, C.POINTER(MoeFfnEpArgs), vp],
         "ztvm_fused_ffn": [vp, C.POINTER(MmDesc), vp, vp, vp, vp, vp, vp],
         "ztvm_silu_mul": [vp, u32, u32, vp, vp, vp],
         "ztvm_moe_combine": [vp, u32, u32, u32, vp, vp, vp, vp],
@@ -218,6 +228,14 @@ class Context:
     def int4_matmul_moe_ep(self, desc: MoeDesc, rows: MoeEpRows, y, x, scales, packed_w, biases, ids, stream=None):
         check(self._lib.ztvm_int4_matmul_moe_ep(self.handle, C.byref(desc), C.byref(rows), ptr(y), ptr(x), ptr(scales),
                                                 ptr(packed_w), ptr(biases), ptr(ids), stream_ptr(stream)))
+
+    def peer_barrier(self, flags, world, rank, stream=None):
+        """flags: every rank's flag-array address as mapped in this process (ints)."""
+        arr = (C.c_void_p * 8)(*[int(f) for f in flags])
+        check(self._lib.ztvm_peer_barrier(self.handle, arr, world, rank, stream_ptr(stream)))
+
+    def moe_ffn_ep(self, args: "MoeFfnEpArgs", stream=None):
+        check(self._lib.ztvm_moe_ffn_ep(self.handle, C.byref(args), stream_ptr(stream)))
 
     def silu_mul_rows(self, rows: MoeEpRows, ffn, h, gate_up, stream=None):
         check(self._lib.ztvm_silu_mul_rows(self.handle, C.byref(rows), ffn, ptr(h), ptr(gate_up), stream_ptr(stream)))

@@ -283,6 +283,64 @@ ztvm_status ztvm_int4_matmul(ztvm_ctx* ctx, const ztvm_mm_desc* d, void* y, cons
   return ZTVM_OK;
 }
 
+ztvm_status ztvm_peer_barrier(ztvm_ctx* ctx, uint32_t* const* flags, uint32_t world, uint32_t rank, void* stream) {
+  ztvm_status s = check_ctx(ctx);
+  if (s) return s;
+  if (!flags) return fail(ZTVM_ERR_NULL_POINTER, "flags is NULL");
+  if (world == 0 || world > 8 || rank >= world) return fail(ZTVM_ERR_BAD_DIMS, "world=%u rank=%u: 1..8 ranks", world, rank);
+  ztvm::PeerBarrierParams p;
+  memset(&p, 0, sizeof(p));
+  for (uint32_t r = 0; r < world; ++r) {
+    if (!flags[r] || !aligned(flags[r], 4)) return fail(ZTVM_ERR_NULL_POINTER, "flags[%u] missing or misaligned", r);
+    p.flags[r] = flags[r];
+  }
+  p.world = world; p.rank = rank;
+  p.wait_cycles = 2000000000ull;      // about a second
+  p.status = ctx->err_counter + 1;
+  cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : ctx->stream;
+  ZTVM_CUDA(ztvm::launch_peer_barrier(p, st));
+  return ZTVM_OK;
+}
+
+ztvm_status ztvm_moe_ffn_ep(ztvm_ctx* ctx, const ztvm_moe_ffn_ep_args* a, void* stream) {
+  ztvm_status s = check_ctx(ctx);
+  if (s) return s;
+  if (!a) return fail(ZTVM_ERR_NULL_POINTER, "args is NULL");
+  const ztvm_moe_ep_layout* L = &a->layout;
+  if (L->world == 0 || L->world > 8 || L->rank >= L->world) return fail(ZTVM_ERR_BAD_DIMS, "world=%u rank=%u: 1..8 ranks", L->world, L->rank);
+  if (!a->gate_up || !a->h) return fail(ZTVM_ERR_NULL_POINTER, "gate_up/h scratch is NULL");
+  if (a->ffn == 0 || a->d == 0) return fail(ZTVM_ERR_BAD_DIMS, "d=%u ffn=%u", a->d, a->ffn);
+  for (uint32_t r = 0; r < L->world; ++r)
+    if (!a->y_slots[r] || !a->flags[r]) return fail(ZTVM_ERR_NULL_POINTER, "y_slots / flags of rank %u missing", r);
+  const uint32_t slots = a->top_k + (a->has_shared ? 1u : 0u);
+  const uint32_t regions = L->world + 1u;
+  const uint64_t rows_total = (uint64_t)regions * L->seg_cap;
+  if (rows_total >= (1ull << 31)) return fail(ZTVM_ERR_TOO_LARGE, "(world + 1) * seg_cap = %llu rows", (unsigned long long)rows_total);
+  if ((s = ztvm_moe_ep_dispatch(ctx, L, a->ids, a->tokens, a->top_k, a->has_shared, a->ids_stride, a->x, a->d, a->x_tok_stride, stream))) return s;
+  if ((s = ztvm_peer_barrier(ctx, a->flags, L->world, L->rank, stream))) return s;
+  ztvm_moe_ep_rows rows;
+  memset(&rows, 0, sizeof(rows));
+  rows.seg_counts = L->recv_cnt[L->rank];
+  rows.seg_cap = L->seg_cap;
+  rows.segments = regions;
+  const uint32_t E1 = L->experts_per_rank + (a->has_shared ? 1u : 0u);
+  ztvm_moe_desc gu = {{a->d, a->ffn, 1, 64, 4, 1, 0}, E1, 1, (uint32_t)rows_total, 0, 2 * a->ffn, a->d, 2 * a->ffn, 1};
+  // a result row goes to y_seg[region] + recv_src[i] * d: recv_src = token * slots + slot indexes rows of d elements
+  ztvm_moe_desc dn = {{a->ffn, a->d, 1, 64, 4, 1, 0}, E1, 1, (uint32_t)rows_total, 0, a->d, a->ffn, a->d, 1};
+  (void)slots;
+  const uint32_t* rids = L->recv_ids[L->rank];
+  if ((s = ztvm_int4_matmul_moe_ep(ctx, &gu, &rows, a->gate_up, L->recv_x[L->rank], a->gate_scales, a->gate_w, a->gate_biases, rids, stream))) return s;
+  rows.reuse_plan = 1;
+  if ((s = ztvm_int4_matmul_moe_ep(ctx, &gu, &rows, static_cast<__half*>(a->gate_up) + a->ffn, L->recv_x[L->rank], a->up_scales, a->up_w,
+                                   a->up_biases, rids, stream))) return s;
+  if ((s = ztvm_silu_mul_rows(ctx, &rows, a->ffn, a->h, a->gate_up, stream))) return s;
+  rows.dst_index = L->recv_src[L->rank];
+  for (uint32_t r = 0; r < L->world; ++r) rows.y_seg[r] = a->y_slots[r];
+  rows.y_seg[L->world] = a->y_slots[L->rank];        // the local region's rows belong to this rank's own tokens
+  if ((s = ztvm_int4_matmul_moe_ep(ctx, &dn, &rows, a->y_slots[L->rank], a->h, a->down_scales, a->down_w, a->down_biases, rids, stream))) return s;
+  return ztvm_peer_barrier(ctx, a->flags, L->world, L->rank, stream);
+}
+
 ztvm_status ztvm_fused_ffn(ztvm_ctx* ctx, const ztvm_mm_desc* d, void* h, const void* x, const void* scales,
                            const void* packed_w, const void* biases, void* stream) {
   ztvm_status s = check_ctx(ctx);

@@ -113,6 +113,14 @@ struct EpDispatchParams {
 };
 cudaError_t launch_moe_ep_dispatch(const EpDispatchParams& p, int sm_count, cudaStream_t st);
 
+struct PeerBarrierParams {
+  uint32_t* flags[8];       // every rank's flag words (world + 1 each), as mapped in this process
+  uint32_t world, rank;
+  unsigned long long wait_cycles;
+  uint32_t* status;
+};
+cudaError_t launch_peer_barrier(const PeerBarrierParams& p, cudaStream_t st);
+
 cudaError_t launch_unpack_codes(const uint32_t* W, uint8_t* codes, uint32_t N, uint32_t K, int bits, cudaStream_t st);
 // The codes as the streaming matrix-unit kernels consume them (in-place f16 subnormals, scaled back to integers).
 cudaError_t launch_unpack_codes_streamed(const uint32_t* W, uint8_t* codes, uint32_t N, uint32_t K, int bits, cudaStream_t st);

@@ -85,4 +85,38 @@ cudaError_t launch_moe_ep_dispatch(const EpDispatchParams& p, int sm_count, cuda
   return cudaGetLastError();
 }
 
+// ---- barrier between ranks ------------------------------------------------------------------------------------------
+// One warp. Lane r deals with rank r: it stores this rank's new epoch into word `rank` of rank r's flag array (release
+// at system scope, after a system fence: whatever this GPU wrote before, peer stores included, is visible to whoever
+// sees the flag) and then waits until word r of its own array has reached the epoch (acquire at system scope). The
+// epoch lives in word `world` of the rank's own array, so replays of a captured graph keep counting. The wait is
+// bounded: when it runs out, the status word is raised and the kernel returns.
+__global__ void __launch_bounds__(32) peer_barrier_kernel(const PeerBarrierParams p) {
+  const uint32_t lane = threadIdx.x;
+  uint32_t epoch = 0;
+  if (lane == 0) {
+    epoch = p.flags[p.rank][p.world] + 1u;
+    p.flags[p.rank][p.world] = epoch;
+  }
+  epoch = __shfl_sync(0xffffffffu, epoch, 0);
+  __threadfence_system();
+  if (lane < p.world) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.flags[lane] + p.rank), "r"(epoch) : "memory");
+    const uint32_t* mine = p.flags[p.rank] + lane;
+    const long long t0 = clock64();
+    while (true) {
+      uint32_t v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+      if ((int32_t)(v - epoch) >= 0) break;
+      if ((unsigned long long)(clock64() - t0) > p.wait_cycles) { atomicExch(p.status, 20u); break; }
+      __nanosleep(200);
+    }
+  }
+}
+
+cudaError_t launch_peer_barrier(const PeerBarrierParams& p, cudaStream_t st) {
+  peer_barrier_kernel<<<1, 32, 0, st>>>(p);
+  return cudaGetLastError();
+}
+
 }  // namespace ztvm

@@ -244,9 +244,11 @@ class ExpertParallelMoE:
     """Expert-parallel form of the block the engine runs as seven dispatches (engine-core.ts:2342-2349)."""
 
     def __init__(self, kernels, gate, up, down, *, E: int, top_k: int, d: int, ffn: int, group=None, max_tokens=None,
-                 peer: bool = True, world: int | None = None, rank: int | None = None):
+                 peer: bool = True, world: int | None = None, rank: int | None = None, one_call: bool = False):
         """gate / up / down: (W, scales, biases) stacks of THIS rank: E/G routed experts followed by the shared one.
-        world / rank: only to stand in for a process group (tests that run several ranks' steps from one process)."""
+        world / rank: only to stand in for a process group (tests that run several ranks' steps from one process).
+        one_call: the peer-store step through ztvm_moe_ffn_ep (dispatch, the library's own device-side barrier, the
+        three projections, barrier) instead of the separate calls with torch's symmetric-memory barrier."""
         self.k, self.group = kernels, group
         self.world = world if world is not None else (dist.get_world_size(group) if dist.is_initialized() else 1)
         self.rank = rank if rank is not None else (dist.get_rank(group) if dist.is_initialized() else 0)
@@ -264,6 +266,7 @@ class ExpertParallelMoE:
                      "projection storing each result row to its source rank -> barrier -> combine" if self.peer else
                      "all-to-all of counts, rows and results (host reads the split sizes)")
         self.capturable = self.world == 1 or self.peer      # no host round trip inside a step
+        self.one_call = bool(one_call) and self.peer
         self._bufs = {}
 
     def _local_block(self, x: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
@@ -292,7 +295,7 @@ class ExpertParallelMoE:
         off_x, off_ids = 0, al(R * d * 2)
         off_src = off_ids + al(R * 4)
         off_cnt = off_src + al(R * 4)
-        off_y = off_cnt + 256
+        off_y = off_cnt + 256          # recv_cnt takes 64 bytes of its 256; the barrier's flag words the next 64
         return off_y + al(T * (K + 1) * d * 2), (off_x, off_ids, off_src, off_cnt, off_y), cap, R
 
     def _peer_state(self, T: int, dev, buf=None, ptrs=None):
@@ -346,6 +349,21 @@ class ExpertParallelMoE:
         st["gu"] = torch.empty((R, 2 * ffn), dtype=torch.float16, device=dev)
         st["h"] = torch.empty((R, ffn), dtype=torch.float16, device=dev)
         st["out"] = torch.empty((T, d), dtype=torch.float16, device=dev)
+        if self.one_call:
+            from .capi import MoeFfnEpArgs
+            a = MoeFfnEpArgs()
+            a.layout = L
+            a.tokens, a.top_k, a.has_shared, a.ids_stride, a.d, a.ffn, a.x_tok_stride = T, K, 1, K + 1, d, ffn, d
+            a.ids = st["ids"].data_ptr()
+            for nm, stack in (("gate", self.gate), ("up", self.up), ("down", self.down)):
+                setattr(a, nm + "_w", stack[0].data_ptr())
+                setattr(a, nm + "_scales", stack[1].data_ptr())
+                setattr(a, nm + "_biases", stack[2].data_ptr())
+            a.gate_up, a.h = st["gu"].data_ptr(), st["h"].data_ptr()
+            for r in range(G):
+                a.y_slots[r] = ptrs[r] + off_y
+                a.flags[r] = ptrs[r] + off_cnt + 64
+            st["args"] = a
         self._bufs[("peer", T)] = st
         return st
 
@@ -355,10 +373,14 @@ class ExpertParallelMoE:
         T, K, d, ffn = x.shape[0], self.top_k, self.d, self.ffn
         st = self._peer_state(T, x.device)
         self.k.route_topk(st["ids"], st["scores"], logits, self.E, K, T)
-        self.k.ep_dispatch(st["layout"], st["ids"], T, K, x, d)
-        st["hdl"].barrier(channel=0)                   # every rank's rows and counts have landed here
-        self._peer_ffn(st)
-        st["hdl"].barrier(channel=1)                   # every result row is back where its token lives
+        if self.one_call:
+            st["args"].x = x.data_ptr()
+            self.k.be.ctx.moe_ffn_ep(st["args"], stream=self.k._stream())
+        else:
+            self.k.ep_dispatch(st["layout"], st["ids"], T, K, x, d)
+            st["hdl"].barrier(channel=0)                   # every rank's rows and counts have landed here
+            self._peer_ffn(st)
+            st["hdl"].barrier(channel=1)                   # every result row is back where its token lives
         self.k.combine(st["out"], st["y_slots"], st["scores"], T, K + 1, d)
         return st["out"]
 
