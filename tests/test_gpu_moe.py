@@ -393,3 +393,33 @@ def test_dispatch_plan_on_the_device_matches_the_tensor_op_plan(backend, dev, T)
     dest = flat[order] // epr
     assert (np.diff(dest) >= 0).all()
     assert np.array_equal(local, (flat[order] % epr).astype(np.int32))
+
+
+def test_peer_barrier_alone_and_with_a_rank_that_never_arrives(backend, dev):
+    """One rank: the barrier passes at once, the epoch counts calls. Two ranks of which the second never calls: the wait
+    is bounded (about a second), the expiry is reported, and the context goes on working afterwards."""
+    import time
+    import torch
+    mine = torch.zeros(16, dtype=torch.int32, device="cuda")
+    for n in range(3):
+        backend.ctx.peer_barrier([mine.data_ptr()], 1, 0)
+    backend.ctx.sync()
+    assert backend.ctx.device_errors() == 0
+    assert mine[0].item() == 3 and mine[1].item() == 3          # word 0: rank 0's arrival, word 1 (= world): the epoch
+    absent = torch.zeros(16, dtype=torch.int32, device="cuda")  # the flag words of a rank that never shows up
+    mine.zero_()
+    t0 = time.perf_counter()
+    backend.ctx.peer_barrier([mine.data_ptr(), absent.data_ptr()], 2, 0)
+    with pytest.raises(z.ZtvmError) as e:
+        backend.ctx.device_errors()
+    waited = time.perf_counter() - t0
+    assert "barrier" in str(e.value) and 0.3 < waited < 10.0, (str(e.value), waited)
+    assert absent[0].item() == 1                                # this rank did announce itself to the other one
+    # the status is cleared by reading it, and ordinary work still runs
+    assert backend.ctx.device_errors() == 0
+    p = z.synth.projection(64, 256, M=1, seed=1)
+    y = dev.empty((1, 64), np.float16)
+    backend.ctx.int4_matmul(z.MmDesc(256, 64, 1, 64, 4, 1, 0), y, dev.put(p["x"]), dev.put(p["scales"]), dev.put(p["W"]),
+                            dev.put(p["biases"]))
+    backend.ctx.sync()
+    assert np.isfinite(dev.get(y)).all()

@@ -867,7 +867,8 @@ ztvm_status ztvm_device_errors(ztvm_ctx* ctx, void* stream, uint32_t* count) {
   ZTVM_CUDA(cudaMemset(ctx->err_counter, 0, 8));
   *count = words[0];
   if (words[1])
-    return fail(ZTVM_ERR_CUDA, "a bounded wait inside the tensor-core GEMM ran out (stage code %u); its output is invalid",
+    return fail(ZTVM_ERR_CUDA, words[1] == 20u ? "a peer barrier gave up waiting for another rank (code %u); what followed it ran on incomplete data"
+                                               : "a bounded wait inside a tensor-core kernel ran out (stage code %u); its output is invalid",
                 words[1]);
   return ZTVM_OK;
 }
