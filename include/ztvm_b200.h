@@ -296,6 +296,12 @@ typedef struct ztvm_moe_ffn_ep_args {
 } ztvm_moe_ffn_ep_args;
 ZTVM_API ztvm_status ztvm_moe_ffn_ep(ztvm_ctx* ctx, const ztvm_moe_ffn_ep_args* args, void* stream);
 
+/* Row-sharded decode projection in one call: ztvm_int4_matmul_multi (this rank's N rows stored into every rank's full
+ * output) followed by ztvm_peer_barrier on `flags`, after which every rank holds the whole [M, N_total] row block. */
+ZTVM_API ztvm_status ztvm_int4_matmul_nshard(ztvm_ctx* ctx, const ztvm_mm_desc* desc, void* const* y_dsts, uint32_t world,
+                                    uint32_t rank, uint32_t y_row_stride, const void* x, const void* scales,
+                                    const void* packed_w, const void* biases, uint32_t* const* flags, void* stream);
+
 /* Fused FFN front half: h[m][i] = f16(up_i * gate_i / (1 + exp(-gate_i))) with gate_i = x[m] . W[i], up_i = x[m] . W[ffn + i],
  * both dot products and the activation in f32, one rounding at the store. `desc->N` is ffn (the output width); the
  * weight, scales and biases hold 2 * ffn rows, gate rows first. Replaces fused_ffn (src/compiler/shaders/fused_ffn.wgsl:

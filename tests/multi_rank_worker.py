@@ -31,14 +31,14 @@ def np_w(t):
     return tuple(a.cpu().numpy().view(np.uint32) if a.dtype == torch.int32 else a.cpu().numpy() for a in t)
 
 
-def projection_with_a_late_consumer(k, dev, rank, world):
+def projection_with_a_late_consumer(k, dev, rank, world, one_call=False):
     N, K, M, steps = 1536, 512, 4, 24
     g = torch.Generator(device=dev)
     g.manual_seed(5)
     W, sc, b = rand_w(g, dev, (), N, K)
     lo, hi = sharded.shard_rows(N, world, rank)
     pj = sharded.NShardedProjection(k, W[lo:hi].contiguous(), sc[lo:hi].contiguous(), b[lo:hi].contiguous(), N, K,
-                                    fused=True, max_m=M)
+                                    fused=True, max_m=M, one_call=one_call)
     xs = torch.randn((steps, M, K), device=dev, generator=g).to(torch.float16)
     consumed = torch.zeros((steps, M, N), dtype=torch.float32, device=dev)
     prev = None
@@ -116,6 +116,7 @@ def main():
     be = z.backend.CudaMatmulBackend(local)
     k = sharded.CudaKernels(be)
     a = projection_with_a_late_consumer(k, dev, rank, world)
+    a = max(a, projection_with_a_late_consumer(k, dev, rank, world, one_call=True))      # ztvm_int4_matmul_nshard
     b = moe_block_by_peer_stores(k, dev, rank, world)
     # the same step as ONE library call per rank (ztvm_moe_ffn_ep) with the library's own device-side barrier
     c = moe_block_by_peer_stores(k, dev, rank, world, one_call=True)

@@ -16,7 +16,7 @@ LIB_PATH = os.environ.get("ZTVM_LIB") or os.path.join(_HERE, "lib", "libztvm_b20
 SYMBOLS = [
     "ztvm_version", "ztvm_status_string", "ztvm_init", "ztvm_destroy", "ztvm_last_error", "ztvm_sync",
     "ztvm_int4_matmul", "ztvm_int4_matmul_multi", "ztvm_int4_matmul_host", "ztvm_int4_matmul_host_async", "ztvm_host_wait", "ztvm_int4_matmul_moe", "ztvm_int4_matmul_moe_noalloc",
-    "ztvm_moe_router_logits", "ztvm_embedding_affine", "ztvm_moe_plan_reuse", "ztvm_moe_route_topk", "ztvm_moe_dispatch_plan", "ztvm_moe_ep_dispatch", "ztvm_int4_matmul_moe_ep", "ztvm_silu_mul_rows", "ztvm_peer_barrier", "ztvm_moe_ffn_ep",
+    "ztvm_moe_router_logits", "ztvm_embedding_affine", "ztvm_moe_plan_reuse", "ztvm_moe_route_topk", "ztvm_moe_dispatch_plan", "ztvm_moe_ep_dispatch", "ztvm_int4_matmul_moe_ep", "ztvm_silu_mul_rows", "ztvm_peer_barrier", "ztvm_moe_ffn_ep", "ztvm_int4_matmul_nshard",
     "ztvm_fused_ffn",
     "ztvm_silu_mul",
     "ztvm_moe_combine", "ztvm_unpack_codes", "ztvm_unpack_codes_streamed", "ztvm_dequant", "ztvm_device_errors",
@@ -101,6 +101,7 @@ def load() -> C.CDLL:
         "ztvm_silu_mul_rows": [vp, C.POINTER(MoeEpRows), u32, vp, vp, vp],
         "ztvm_peer_barrier": [vp, C.POINTER(C.c_void_p), u32, u32, vp],
         "ztvm_moe_ffn_ep": [vp, C.POINTER(MoeFfnEpArgs), vp],
+        "ztvm_int4_matmul_nshard": [vp, C.POINTER(MmDesc), C.POINTER(C.c_void_p), u32, u32, u32, vp, vp, vp, vp, C.POINTER(C.c_void_p), vp],
         "ztvm_fused_ffn": [vp, C.POINTER(MmDesc), vp, vp, vp, vp, vp, vp],
         "ztvm_silu_mul": [vp, u32, u32, vp, vp, vp],
         "ztvm_moe_combine": [vp, u32, u32, u32, vp, vp, vp, vp],
@@ -233,6 +234,13 @@ class Context:
         """flags: every rank's flag-array address as mapped in this process (ints)."""
         arr = (C.c_void_p * 8)(*[int(f) for f in flags])
         check(self._lib.ztvm_peer_barrier(self.handle, arr, world, rank, stream_ptr(stream)))
+
+    def int4_matmul_nshard(self, desc: MmDesc, y_dsts, world, rank, y_row_stride, x, scales, packed_w, biases, flags, stream=None):
+        """ztvm_int4_matmul_multi + ztvm_peer_barrier: y_dsts / flags are every rank's addresses as mapped here (ints)."""
+        ya = (C.c_void_p * 8)(*[int(v) for v in y_dsts])
+        fa = (C.c_void_p * 8)(*[int(v) for v in flags])
+        check(self._lib.ztvm_int4_matmul_nshard(self.handle, C.byref(desc), ya, world, rank, y_row_stride, ptr(x), ptr(scales),
+                                                ptr(packed_w), ptr(biases), fa, stream_ptr(stream)))
 
     def moe_ffn_ep(self, args: "MoeFfnEpArgs", stream=None):
         check(self._lib.ztvm_moe_ffn_ep(self.handle, C.byref(args), stream_ptr(stream)))

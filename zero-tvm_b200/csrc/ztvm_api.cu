@@ -302,6 +302,17 @@ ztvm_status ztvm_peer_barrier(ztvm_ctx* ctx, uint32_t* const* flags, uint32_t wo
   return ZTVM_OK;
 }
 
+ztvm_status ztvm_int4_matmul_nshard(ztvm_ctx* ctx, const ztvm_mm_desc* d, void* const* y_dsts, uint32_t world, uint32_t rank,
+                                    uint32_t y_row_stride, const void* x, const void* scales, const void* packed_w,
+                                    const void* biases, uint32_t* const* flags, void* stream) {
+  ztvm_status s = check_ctx(ctx);
+  if (s) return s;
+  if (world == 0 || world > 8 || rank >= world) return fail(ZTVM_ERR_BAD_DIMS, "world=%u rank=%u: 1..8 ranks", world, rank);
+  // a rank whose shard is empty (N_total smaller than the rank count allows) still takes part in the barrier
+  if (d && d->N > 0 && (s = ztvm_int4_matmul_multi(ctx, d, y_dsts, world, y_row_stride, x, scales, packed_w, biases, stream))) return s;
+  return ztvm_peer_barrier(ctx, flags, world, rank, stream);
+}
+
 ztvm_status ztvm_moe_ffn_ep(ztvm_ctx* ctx, const ztvm_moe_ffn_ep_args* a, void* stream) {
   ztvm_status s = check_ctx(ctx);
   if (s) return s;

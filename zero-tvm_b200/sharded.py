@@ -157,7 +157,7 @@ class NShardedProjection:
     """
 
     def __init__(self, kernels, W, scales, biases, N_total: int, K: int, *, out_f32: bool = False, group=None,
-                 fused: bool = False, max_m: int = 8):
+                 fused: bool = False, max_m: int = 8, one_call: bool = False):
         self.k, self.group = kernels, group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -179,6 +179,14 @@ class NShardedProjection:
             # address of (buffer b, row 0, column lo) inside every rank's copy
             self._dst = [[int(base) + (bi * max_m * N_total + self.lo) * esz for base in self._hdl.buffer_ptrs]
                          for bi in range(3)]
+            # one_call: ztvm_int4_matmul_nshard (the GEMV's peer stores + the library's own device-side barrier) instead of
+            # the GEMV followed by torch's symmetric-memory barrier; the flag words are a symmetric allocation of their own
+            self.one_call = bool(one_call)
+            if self.one_call:
+                self._flag_buf = symm.empty((64,), dtype=torch.int32, device=W.device)
+                self._flag_buf.zero_()
+                self._flags = [int(p) for p in symm.rendezvous(self._flag_buf, g.group_name).buffer_ptrs]
+                dist.barrier(group=group)          # every rank's flag words are zero before anyone's first store
 
     def forward(self, x: torch.Tensor, M: int) -> torch.Tensor:
         """x f16 [M, K] (replicated) -> y [M, N_total], every rank holding the whole output."""
@@ -186,6 +194,12 @@ class NShardedProjection:
             assert M <= self.max_m
             bi = self._flip
             self._flip = (bi + 1) % 3
+            if self.one_call:
+                from .capi import MmDesc
+                self.k.be.ctx.int4_matmul_nshard(MmDesc(self.K, self.hi - self.lo, M, 64, 4, 1, int(self.out_f32)), self._dst[bi],
+                                                 self.world, self.rank, self.N_total, x, self.s, self.W, self.b, self._flags,
+                                                 stream=self.k._stream())
+                return self._out[bi, :M]
             if self.hi > self.lo:
                 self.k.matmul_multi(self._dst[bi], self.N_total, x, self.W, self.s, self.b, self.hi - self.lo, self.K, M,
                                     self.out_f32)
