@@ -18,7 +18,7 @@ def moe_kernel_kind(pairs, experts, K, N, bits):
         return "pair"
     tiles_ok = K % 64 == 0 and N % 8 == 0
     stream_ok = K % 256 == 0 and K <= 4096 and N % 16 == 0
-    if stream_ok and (pairs < 24 * experts or not tiles_ok):
+    if stream_ok and (pairs < 10 * experts or not tiles_ok):
         return "stream"
     return "tiles" if tiles_ok else "pair"
 
@@ -271,8 +271,9 @@ def test_plan_reuse_across_the_matmuls_of_one_step(backend, dev, oracle_c):
         assert np.array_equal(outs[(False, li)][0], outs[(True, li)][0])
         assert np.array_equal(outs[(False, li)][1], outs[(True, li)][1])
         idn = outs[(True, li)][2]
-        ref = oracle_c.moe_matmul_f64(mb["x"], *mb["up"], idn, 256, 512, 64, 4, in_per_slot=False, w16=False)
-        err = zo.rel_err_scaled(outs[(True, li)][1].view(np.float16), ref, 1e-3)
+        tiles = moe_kernel_kind(64 * slots, 17, 512, 256, 4) == "tiles"
+        ref = oracle_c.moe_matmul_f64(mb["x"], *mb["up"], idn, 256, 512, 64, 4, in_per_slot=False, w16=tiles)
+        err = zo.rel_err_scaled(outs[(True, li)][1].view(np.float16), ref, 1e-2 if tiles else 1e-3)
         record_parity(err, zo.rel_err(outs[(True, li)][1].view(np.float16), ref))
         assert err <= TOL
     assert not np.array_equal(outs[(True, 0)][2], outs[(True, 1)][2])

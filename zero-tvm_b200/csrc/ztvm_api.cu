@@ -525,7 +525,12 @@ static int moe_pick(const ztvm_ctx* ctx, const ztvm_moe_desc* md, const ztvm::Ge
                      ztvm::moe_grouped_supported((int)d->bits, d->group, d->K, d->N, md->experts);
   const int tiles = ctx->moe_tiles_sm ? (sm_ok ? 3 : ta_ok ? 1 : 0) : (ta_ok ? 1 : sm_ok ? 3 : 0);
   const bool stream_ok = ztvm::moe_tc_supported(p, (int)d->bits) && !p.dst_index;
-  const bool few_per_expert = pairs < 24ull * md->experts;
+  // Where the two grouped kernels cross (measured on the 257-expert block, hidden 2048, ffn 512): the tiles cost the same
+  // whatever the pair count (every expert's weights are dequantised once: ~100 us per projection), the streaming kernel
+  // grows with the 8-pair chunks it walks (gate: 35 us + 0.020 us per pair; down, with its short K: 48 us + 0.028 us per
+  // pair). They meet near 12.6 pairs per expert for the long-K projections and 6.6 for the short-K one; one threshold
+  // for both keeps the three projections of a block on one kernel, whose plan they can then share.
+  const bool few_per_expert = pairs < 10ull * md->experts;
   if (forced == 1) return tiles ? tiles : stream_ok ? 2 : 0;
   if (forced == 2) return stream_ok ? 2 : tiles;
   return (stream_ok && (few_per_expert || !tiles)) ? 2 : tiles;
