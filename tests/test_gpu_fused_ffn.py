@@ -36,6 +36,17 @@ def test_paired_gemv_against_the_anchor(ffn, K, M, backend, dev):
     assert err <= TOL, err
 
 
+def test_paired_gemv_symmetric_flavour(backend, dev):
+    """w = s * (q - 7) at group 64 takes the one-launch form too (the reference's fused_ffn is symmetric, at group 32)."""
+    ffn, K, M = 640, 1024, 2
+    p = z.synth.projection(2 * ffn, K, M=M, seed=91, affine=False)
+    got = run_fused(backend, dev, p, ffn, M).astype(np.float64)
+    ref = zo.fused_ffn_f64(p["x"], p["W"], p["scales"], p["biases"], ffn, 64, 4, False)
+    err = zo.rel_err_scaled(got, ref, 1e-3)
+    record_parity(err, zo.rel_err(got, ref))
+    assert np.isfinite(got).all() and err <= TOL, err
+
+
 def test_small_case_matches_the_shader_arithmetic(backend, dev):
     """Against the shader's own order of operations in f32 (word-order dot products, f32 SiLU, one f16 rounding):
     at most one f16 unit in the last place apart on all but a few outputs, none further than 2e-3."""
