@@ -6,13 +6,19 @@ package imports it; only the test-suite, the smoke check and the CPU-baseline
 leg of the benchmark do, and always as the checker, never as the thing being
 measured or shipped.
 
-Parity status. The 4-bit affine dequantiser is pinned against the reference's
-own numpy `dequant_from` (scripts/make-dsv2-layer-ref.py:102-116) through the
-committed fixtures in tests/golden/. Everything else (3-bit bitstream, the
-symmetric flavour, the GEMV word order, routing, SiLU, combine) follows the
-reference's formulas but the reference ships no stored vectors for them and its
-JavaScript/WGSL cannot run here: for those functions parity is pinned by
-formula only ("parity unpinned" against executed reference output).
+Parity status. Pinned against output of the reference's own numpy code, run on
+seeded inputs and committed as fixtures in tests/golden/ (made by
+tests/golden/make_golden.py, which extracts the pieces with `ast`): the 4-bit
+affine dequantiser (`dequant_from`, scripts/make-dsv2-layer-ref.py:102-116), the
+3-bit and 4-bit unpack and the factored GEMV reference
+(scripts/make-kernel-ref.py:55-66), the routing of one token (softmax, top-k
+order with ties to the lower index, raw or renormalised weights:
+scripts/make-dsv2-layer-ref.py:327-345) and `silu_mul` (:283-284). Everything
+else (the symmetric flavour, the GEMV word order, the shared-expert slot, combine,
+router logits, embedding, fused FFN) follows the reference's formulas, but the
+reference ships no stored vectors for them and its JavaScript/WGSL cannot run
+here: for those functions parity is pinned by formula only ("parity unpinned"
+against executed reference output).
 
 Every function cites the reference file:line it follows (paths are relative to
 the reference project's root).

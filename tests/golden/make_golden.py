@@ -21,10 +21,21 @@ opens a checkpoint (both absent here). The statements that follow (lines 55-66: 
 LSB-first bit-stream unpack, then `xg`, `dot`, `y` = sum_g s_g*dot_g + b_g*xsum_g) are pure numpy. They are
 located with `ast` inside that function (the `if bits == 4` statement and the assignments to xg, dot, y), compiled on
 their own and executed on seeded Wq / scales / biases / x. Stored: the inputs, the codes `nib` and `y` they produced.
+
+silu_mul_ref.npz
+`scripts/make-dsv2-layer-ref.py:283-284` `silu_mul(gate, up)` is a two-line numpy function; it is located with `ast`
+and run on seeded f32 inputs that hold f16 values (what the engine's silu_mul kernel reads), large magnitudes included.
+
+router_ref_*.npz
+The same script routes one token in plain numpy at module level (lines 327-345: softmax over all experts, stable
+arg-sort for a DESCENDING order with ties to the lower index, the K weights scaled and optionally renormalised). Those
+statements (the assignments to probs, ids, topk_w, the `probs /= ...` and the `if args.norm_topk_prob`) are located
+with `ast`, compiled on their own and executed once per token on seeded logits, some with exact ties.
 """
 import ast
 import os
 import sys
+import types
 
 import numpy as np
 
@@ -87,10 +98,63 @@ def make_kernel_ref(ref_root: str):
         print(name, Wq.shape, "-> codes", nib.shape, "y", y.shape)
 
 
+def make_silu_mul(ref_root: str):
+    path = os.path.join(ref_root, "scripts", "make-dsv2-layer-ref.py")
+    tree = ast.parse(open(path).read())
+    fn = next(n for n in tree.body if isinstance(n, ast.FunctionDef) and n.name == "silu_mul")
+    ns = {"np": np}
+    exec(compile(ast.Module(body=[fn], type_ignores=[]), path, "exec"), ns)
+    rng = np.random.default_rng(31)
+    gate = (rng.standard_normal((64, 96)) * 3.0).astype(np.float16)
+    up = (rng.standard_normal((64, 96)) * 2.0).astype(np.float16)
+    gate[0, :8] = np.array([0.0, -0.0, 12.0, -12.0, 30.0, -30.0, 6.1e-5, -6.1e-5], dtype=np.float16)
+    h = ns["silu_mul"](gate.astype(np.float32), up.astype(np.float32))
+    assert h.dtype == np.float32 and h.shape == gate.shape
+    np.savez_compressed(os.path.join(HERE, "silu_mul_ref.npz"), gate=gate, up=up, h=h)
+    print("silu_mul", gate.shape, "->", h.shape)
+
+
+def make_router(ref_root: str):
+    path = os.path.join(ref_root, "scripts", "make-dsv2-layer-ref.py")
+    tree = ast.parse(open(path).read())
+    picked = []
+    for node in ast.walk(tree):
+        if isinstance(node, ast.If) and isinstance(node.test, ast.UnaryOp) and getattr(node.test.operand, "id", "") == "MOE":
+            for st in node.orelse:                       # the MoE branch, in source order
+                if isinstance(st, ast.Assign) and getattr(st.targets[0], "id", "") in ("probs", "ids", "topk_w"):
+                    picked.append(st)
+                elif isinstance(st, ast.AugAssign) and getattr(st.target, "id", "") == "probs":
+                    picked.append(st)
+                elif isinstance(st, ast.If) and "norm_topk_prob" in ast.dump(st.test):
+                    picked.append(st)
+    kinds = [type(n).__name__ + ":" + (getattr(getattr(n, "targets", [None])[0], "id", "") if isinstance(n, ast.Assign) else "") for n in picked]
+    assert kinds == ["Assign:probs", "AugAssign:", "Assign:ids", "Assign:topk_w", "If:"], kinds
+    code = compile(ast.Module(body=picked, type_ignores=[]), path, "exec")
+    for name, (T, E, K, seed, norm) in {"e64_k6_raw": (24, 64, 6, 41, False), "e256_k8_norm": (24, 256, 8, 42, True),
+                                        "e16_k4_norm": (12, 16, 4, 43, True)}.items():
+        rng = np.random.default_rng(seed)
+        logits = rng.standard_normal((T, E)).astype(np.float32)
+        logits[1, 5] = logits[1, 3]                      # exact ties: the lower index must come first
+        logits[2, E - 1] = logits[2, 0] = logits[2].max() + np.float32(0.5)
+        logits[3, :] = np.float32(0.25)                  # all equal: experts 0..K-1 in order
+        ids = np.zeros((T, K), dtype=np.uint32)
+        w = np.zeros((T, K), dtype=np.float32)
+        for t in range(T):
+            ns = {"np": np, "router_logits": logits[t].copy(), "K": K,
+                  "args": types.SimpleNamespace(routed_scaling=1.0, norm_topk_prob=norm)}
+            exec(code, ns)
+            ids[t], w[t] = ns["ids"], ns["topk_w"].astype(np.float32)
+        np.savez_compressed(os.path.join(HERE, f"router_ref_{name}.npz"), logits=logits, ids=ids, weights=w,
+                            norm=np.int32(norm))
+        print("router", name, logits.shape, "->", ids.shape)
+
+
 def main():
     if len(sys.argv) < 2:
         raise SystemExit("usage: make_golden.py <path to a checkout of the reference project>")
     ref_root = sys.argv[1]
+    make_silu_mul(ref_root)
+    make_router(ref_root)
     make_kernel_ref(ref_root)
     dequant_from = load_dequant_from(ref_root)
     cases = {

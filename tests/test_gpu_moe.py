@@ -424,3 +424,38 @@ def test_peer_barrier_alone_and_with_a_rank_that_never_arrives(backend, dev):
                             dev.put(p["biases"]))
     backend.ctx.sync()
     assert np.isfinite(dev.get(y)).all()
+
+
+def _golden(name):
+    import os
+    return np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", name))
+
+
+@pytest.mark.parametrize("name", ["router_ref_e64_k6_raw.npz", "router_ref_e256_k8_norm.npz", "router_ref_e16_k4_norm.npz"])
+def test_router_kernel_against_the_reference_numpy_router(name, backend, dev):
+    """ztvm_moe_route_topk on the vectors the reference's own numpy routing produced (see tests/golden/make_golden.py):
+    the same experts in the same slots, exact ties included, and the same weights."""
+    g = _golden(name)
+    logits, ids, w, norm = g["logits"], g["ids"], g["weights"], bool(g["norm"])
+    T, E = logits.shape
+    K = ids.shape[1]
+    d_ids = dev.empty((T, K), np.uint32, fill=0)
+    d_w = dev.empty((T, K), np.float32, fill=0.0)
+    backend.moe_router_topk(d_ids, d_w, dev.put(logits), E, K, norm, False, T)
+    backend.ctx.sync()
+    assert np.array_equal(dev.get(d_ids, np.uint32), ids)
+    assert np.allclose(dev.get(d_w), w, rtol=3e-6, atol=1e-9)
+
+
+def test_silu_kernel_against_the_reference_numpy_function(backend, dev):
+    """ztvm_silu_mul on the inputs of the reference's numpy silu_mul: its f32 value rounded to f16, at most one f16 step
+    away where the kernel's order of the three operations rounds differently."""
+    g = _golden("silu_mul_ref.npz")
+    gate, up, h = g["gate"], g["up"], g["h"]
+    rows, ffn = gate.shape
+    out = dev.empty((rows, ffn), np.float16, fill=float("nan"))
+    backend.silu_mul(out, dev.put(np.ascontiguousarray(np.concatenate([gate, up], axis=1))), rows, ffn)
+    backend.ctx.sync()
+    got, want = dev.get(out), h.astype(np.float16)
+    steps = np.abs(got.view(np.int16).astype(np.int32) - want.view(np.int16).astype(np.int32))
+    assert steps.max() <= 1 and (steps == 0).mean() >= 0.99, (steps.max(), (steps == 0).mean())

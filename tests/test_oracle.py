@@ -224,3 +224,38 @@ def test_fused_ffn_restatements_agree():
         assert zo.rel_err_scaled(b.astype(np.float64), a, 1e-3) <= 2e-3
         y = zo.matmul_f64(p["x"], zo.dequant_w32(zo.unpack_codes(p["W"], 4), p["scales"], p["biases"], group, affine))
         assert np.allclose(a, y[:, 48:] * y[:, :48] / (1 + np.exp(-y[:, :48])), rtol=1e-12)
+
+
+def _golden(name):
+    import os
+    return np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", name))
+
+
+@pytest.mark.parametrize("name", ["router_ref_e64_k6_raw.npz", "router_ref_e256_k8_norm.npz", "router_ref_e16_k4_norm.npz"])
+def test_router_against_the_reference_numpy_router(name):
+    """Vectors made by the reference's own numpy routing statements (scripts/make-dsv2-layer-ref.py:327-345; extracted
+    with ast by tests/golden/make_golden.py): same experts in the same slot order -- ties to the lower index included --
+    and the same weights, with and without renormalisation, from both restatements."""
+    from oracle import ztvm_oracle_c as zc
+    g = _golden(name)
+    logits, ids, w, norm = g["logits"], g["ids"], g["weights"], bool(g["norm"])
+    T, E = logits.shape
+    K = ids.shape[1]
+    for fn in (zo.router_topk, zc.router_topk):
+        got_ids, got_w = fn(logits, E, K, norm, False)
+        assert np.array_equal(np.asarray(got_ids, dtype=np.uint32), ids), fn.__module__
+        assert np.allclose(got_w, w, rtol=2e-6, atol=1e-9), fn.__module__
+
+
+def test_silu_mul_against_the_reference_numpy_function():
+    """silu_mul of scripts/make-dsv2-layer-ref.py:283-284 run on f32 copies of f16 inputs: the restatements round its
+    value to f16; another order of the same three operations may land one f16 step away on a few outputs."""
+    from oracle import ztvm_oracle_c as zc
+    g = _golden("silu_mul_ref.npz")
+    gate, up, h = g["gate"], g["up"], g["h"]
+    want = h.astype(np.float16)
+    gu = np.concatenate([gate, up], axis=1)
+    for fn in (zo.silu_mul, zc.silu_mul):
+        got = np.asarray(fn(gu, gate.shape[1]), dtype=np.float16)
+        steps = np.abs(got.view(np.int16).astype(np.int32) - want.view(np.int16).astype(np.int32))
+        assert steps.max() <= 1 and (steps == 0).mean() >= 0.99, (fn.__module__, steps.max(), (steps == 0).mean())
