@@ -83,7 +83,7 @@ class ClockSampler:
          "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
-        self.rows, self.proc, self.index = [], None, index
+        self.rows, self.proc, self.index, self.skip = [], None, index, 0
 
     def __enter__(self):
         try:
@@ -92,9 +92,19 @@ class ClockSampler:
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
+            # nvidia-smi takes its time to produce the first row (seconds when eight ranks start one each): the timed
+            # region begins only once sampling is live, and rows from before it are not counted
+            t0 = time.perf_counter()
+            while not self.rows and time.perf_counter() - t0 < 8.0 and self.proc.poll() is None:
+                time.sleep(0.01)
+            self.skip = len(self.rows)
         except OSError:
             self.proc = None
         return self
+
+    def mark(self):
+        """The timed region starts now: rows read so far do not count."""
+        self.skip = len(self.rows)
 
     def _read(self):
         for line in self.proc.stdout:
@@ -110,7 +120,7 @@ class ClockSampler:
                 self.proc.kill()
 
     def summary(self):
-        ok = [r for r in self.rows if len(r) >= 8 and r[0].isdigit()]
+        ok = [r for r in self.rows[self.skip:] if len(r) >= 8 and r[0].isdigit()]
         if not ok:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
         reasons = set()
@@ -304,12 +314,13 @@ class ShardedBench:
             for _ in range(2):
                 replay.replay()
             torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
         n = -(-self.steps // per_replay)
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with ClockSampler(self.local) as clocks:
+        with ClockSampler(self.local) as clocks:      # sampling is live when this returns; the ranks meet after that
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            clocks.mark()
             ev0.record()
             for _ in range(n):
                 if replay is not None:
@@ -664,9 +675,11 @@ def main():
             pt = torch.tensor([passes], device=device)
             dist.all_reduce(pt, op=dist.ReduceOp.MAX)
             passes = int(pt.item())
-            dist.barrier()
-        torch.cuda.synchronize()
-        with ClockSampler(local) as clocks:
+        with ClockSampler(local) as clocks:      # sampling is live when this returns; the ranks meet after that
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            clocks.mark()
             ev0.record(stream)
             for _ in range(args.steps * passes):
                 graph.replay()
