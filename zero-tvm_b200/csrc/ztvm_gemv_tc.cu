@@ -93,15 +93,29 @@ gemv_tc_kernel(const GemvParams p) {
   const uint32_t sb_dst = kTcTileW + sb_row * 16 + sb_which * 8;
   const size_t row4 = (size_t)4 * p.KP;
   uint32_t i_step = 0, i_kt = 0, i_rd = 0;                  // the next step to issue, as (K tile, round)
+  // Running addresses of this lane's pieces of the next tile (plain form: rows advance by RG tiles per round, slices
+  // by KS per K tile), so a step costs a few adds instead of 64-bit multiplies; the paired form computes its rows.
+  const uint32_t* const src_base = p.W + (size_t)(r0 + rg * 16 + cp_row) * p.KP + ks * 32 + cp_chunk * 4;
+  const __half* const sb_base = (sb_which ? p.B : p.S) + (size_t)(r0 + rg * 16 + sb_row) * p.SPR + ks * 4;
+  const size_t src_round = (size_t)RG * 16 * p.KP, sb_round = (size_t)RG * 16 * p.SPR;
+  const uint32_t* src_run = src_base;
+  const __half* sb_run = sb_base;
+  uint32_t i_trow = rg * 16, i_slot = 0;
   auto issue = [&]() {
     if (warp_active && i_step < total) {
       const uint32_t sl = i_kt * KS + ks;
-      const uint32_t trow = (i_rd * RG + rg) * 16;          // first row of the tile, CTA-relative
+      const uint32_t trow = i_trow;                         // first row of the tile, CTA-relative
       if (sl < slices && trow < nrows) {
-        const uint32_t st = ring + (i_step % kTcDepth) * kTcTileBytes;
-        const uint32_t wrow = tile_row(trow), live = tile_live(trow);
-        const uint32_t* src = p.W + (size_t)(wrow + cp_row) * p.KP + sl * 32 + cp_chunk * 4;
-        const __half* sbp = (sb_which ? p.B : p.S) + (size_t)(wrow + sb_row) * p.SPR + sl * 4;
+        const uint32_t st = ring + i_slot * kTcTileBytes;
+        const uint32_t* src = src_run;
+        const __half* sbp = sb_run;
+        uint32_t live = nrows - trow < 16u ? nrows - trow : 16u;
+        if (paired) {
+          const uint32_t wrow = tile_row(trow);
+          live = tile_live(trow);
+          src = p.W + (size_t)(wrow + cp_row) * p.KP + sl * 32 + cp_chunk * 4;
+          sbp = (sb_which ? p.B : p.S) + (size_t)(wrow + sb_row) * p.SPR + sl * 4;
+        }
         if (live == 16u) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) tc_cp16(st + cp_dst + i * 512, src + i * row4);   // (row + 4i) & 3 == row & 3
@@ -116,7 +130,14 @@ gemv_tc_kernel(const GemvParams p) {
     }
     tc_commit();
     ++i_step;
-    if (++i_rd == rounds) { i_rd = 0; ++i_kt; }
+    if (++i_slot == (uint32_t)kTcDepth) i_slot = 0;
+    src_run += src_round; sb_run += sb_round; i_trow += RG * 16;
+    if (++i_rd == rounds) {
+      i_rd = 0; ++i_kt;
+      i_trow = rg * 16;
+      src_run = src_base + (size_t)i_kt * KS * 32;
+      sb_run = sb_base + (size_t)i_kt * KS * 4;
+    }
   };
 #pragma unroll
   for (int i = 0; i < kTcDepth - 1; ++i) issue();
