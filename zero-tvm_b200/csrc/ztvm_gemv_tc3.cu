@@ -63,25 +63,43 @@ gemv_tc3_kernel(const GemvParams p) {   // 3-bit weights exist only in the affin
   const uint32_t sb_row = (uint32_t)lane >> 1, sb_which = (uint32_t)lane & 1;
   const uint32_t sb_dst = kT3TileW + sb_row * 16 + sb_which * 8;
   uint32_t i_step = 0, i_kt = 0, i_rd = 0;
+  // this lane's three 16-byte pieces of a tile (row, chunk) and their running source addresses: rows advance by RG tiles
+  // per round, slices by KS per K tile
+  uint32_t cp_row3[3], cp_dst3[3];
+  const uint32_t* src_base[3];
+#pragma unroll
+  for (int i = 0; i < 3; ++i) {
+    const uint32_t q = (uint32_t)lane + 32u * i, row = q / 6, j = q - row * 6;
+    cp_row3[i] = row;
+    cp_dst3[i] = row * kT3RowBytes + j * 16;
+    src_base[i] = p.W + (size_t)(r0 + rg * 16 + row) * p.KP + ks * 24 + j * 4;
+  }
+  const __half* const sb_base = (sb_which ? p.B : p.S) + (size_t)(r0 + rg * 16 + sb_row) * p.SPR + ks * 4;
+  const size_t src_round = (size_t)RG * 16 * p.KP, sb_round = (size_t)RG * 16 * p.SPR;
+  size_t src_off = 0, sb_off = 0;
+  uint32_t i_trow = rg * 16, i_slot = 0;
   auto issue = [&]() {
     if (warp_active && i_step < total) {
       const uint32_t sl = i_kt * KS + ks;
-      const uint32_t trow = (i_rd * RG + rg) * 16;
+      const uint32_t trow = i_trow;
       if (sl < slices && trow < nrows) {
-        const uint32_t st = ring + (i_step % kTcDepth) * kT3TileBytes;
+        const uint32_t st = ring + i_slot * kT3TileBytes;
 #pragma unroll
-        for (int i = 0; i < 3; ++i) {
-          const uint32_t q = (uint32_t)lane + 32u * i, row = q / 6, j = q - row * 6;
-          if (trow + row < nrows)
-            tc_cp16(st + row * kT3RowBytes + j * 16, p.W + (size_t)(r0 + trow + row) * p.KP + sl * 24 + j * 4);
-        }
-        if (trow + sb_row < nrows)
-          tc_cp8(st + sb_dst, (sb_which ? p.B : p.S) + (size_t)(r0 + trow + sb_row) * p.SPR + sl * 4);
+        for (int i = 0; i < 3; ++i)
+          if (trow + cp_row3[i] < nrows) tc_cp16(st + cp_dst3[i], src_base[i] + src_off);
+        if (trow + sb_row < nrows) tc_cp8(st + sb_dst, sb_base + sb_off);
       }
     }
     tc_commit();
     ++i_step;
-    if (++i_rd == rounds) { i_rd = 0; ++i_kt; }
+    if (++i_slot == (uint32_t)kTcDepth) i_slot = 0;
+    src_off += src_round; sb_off += sb_round; i_trow += RG * 16;
+    if (++i_rd == rounds) {
+      i_rd = 0; ++i_kt;
+      i_trow = rg * 16;
+      src_off = (size_t)i_kt * KS * 24;
+      sb_off = (size_t)i_kt * KS * 4;
+    }
   };
 #pragma unroll
   for (int i = 0; i < kTcDepth - 1; ++i) issue();
