@@ -245,3 +245,21 @@ def test_resolve_matmul_for_spec_and_int8_entries():
     for name, m_rows in (("int8_affine_matvec", False), ("int8_affine_batched", True)):
         info = parse_entry(name)
         assert info.bits == 8 and info.affine and info.has_m_rows == m_rows and not info.moe
+
+
+def test_public_header_is_plain_c():
+    """include/ztvm_b200.h is the binding surface for cgo / N-API / ctypes style callers: it must compile as C99 by itself."""
+    import os
+    import shutil
+    import subprocess
+    import tempfile
+    if not shutil.which("gcc"):
+        pytest.skip("no C compiler")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    with tempfile.TemporaryDirectory() as d:
+        src = os.path.join(d, "hdr.c")
+        with open(src, "w") as fh:
+            fh.write('#include "ztvm_b200.h"\nint main(void) { ztvm_mm_desc d = {0}; (void)d; return 0; }\n')
+        r = subprocess.run(["gcc", "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-fsyntax-only",
+                            "-I", os.path.join(root, "include"), src], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
